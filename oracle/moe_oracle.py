@@ -1,0 +1,254 @@
+"""Per-expert restatement of the reference's torch oracle (test infrastructure only).
+
+Every function names the reference lines it follows (paths relative to the
+ROCm/aiter tree).  The reference dequantises all experts to fp32 at once
+(``aiter/fused_moe.py:3581,3589-3594,3724,3737-3743``), ~60 GB for a
+DeepSeek-V3 ``w1``; here the same element-wise arithmetic and the same
+``sub_tokens @ w_e.T`` matmuls are issued one expert at a time, which is
+bit-identical on CPU (checked by ``tests/golden/make_golden.py``).
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.nn.functional as F
+
+FP8 = torch.float8_e4m3fn
+FP8_MAX = 448.0  # torch.finfo(float8_e4m3fn).max
+
+
+# --------------------------------------------------------------------------- quantisers
+def _pertoken_quant(x: torch.Tensor, quant_dtype=FP8):
+    """aiter/ops/quant.py:64-94 (pertoken_quant, scale=None, x_scale=None).
+
+    amax over the last dim -> scale = amax / dtypeMax (true division), zero
+    scales become 1, codes = (x / scale) cast to the quant dtype (RNE).
+    """
+    x = x.to(torch.float32)
+    amax, _ = torch.max(torch.abs(x), dim=-1, keepdim=True)
+    scale = amax / FP8_MAX
+    scale[scale == 0] = 1
+    y = (x / scale).to(dtype=quant_dtype)
+    return y, scale.to(torch.float32)
+
+
+def quant_1x128(x: torch.Tensor):
+    """1x128 activation quant as the 2-stage test does it:
+    op_tests/test_moe_2stage.py:237-242 (a1) and :419-423 (a2).
+    ``x`` [R, C] -> codes [R, C] e4m3, scales [R, C/128] fp32."""
+    R, C = x.shape
+    q, s = _pertoken_quant(x.reshape(R, -1, 128))
+    return q.view(R, C), s.squeeze(-1)
+
+
+def quant_weight_128x128(w: torch.Tensor):
+    """op_tests/test_moe_2stage.py:184-208 (weight_per_128x128_quant).
+    ``w`` [E, N, K] -> codes [E, N, K] e4m3, scales [E, N/128, K/128] fp32."""
+    E, d1, d2 = w.shape
+    blocks = w.view(E, d1 // 128, 128, d2 // 128, 128).permute(0, 1, 3, 2, 4).contiguous()
+    blocks = blocks.view(E, -1, 128 * 128)
+    q, s = _pertoken_quant(blocks)
+    q = q.view(E, d1 // 128, d2 // 128, 128, 128).permute(0, 1, 3, 2, 4).contiguous()
+    return q.view(E, d1, d2), s.view(E, d1 // 128, d2 // 128)
+
+
+def quant_per_token(x: torch.Tensor):
+    """get_torch_quant(per_Token): pertoken_quant over the last dim
+    (aiter/ops/quant.py:349-364; used by op_tests/test_moe_2stage.py:213-214,264)."""
+    return _pertoken_quant(x)
+
+
+# --------------------------------------------------------------------------- sorting
+def moe_sorting_ref(topk_ids, topk_weights, num_experts, block_size,
+                    expert_mask=None, num_local_tokens=None):
+    """op_tests/test_moe_sorting.py:45-99 (run_torch_moe_sorting).
+
+    Stable bucket sort of (token, slot) by expert, each expert padded to a
+    multiple of ``block_size``; ids pack ``slot << 24 | token``; pad entries are
+    ``topk << 24 | M`` with M the static row count; experts without routes get
+    no block; masked experts are dropped and the rest renumbered.
+    Slots that the reference leaves unwritten (weights of pads, ids past the
+    padded total) are returned as 0.0 / pad-id / -1."""
+    m, topk = topk_ids.shape
+    max_padded = topk_ids.numel() + num_experts * block_size - topk
+    max_blocks = (max_padded + block_size - 1) // block_size
+    init_val = topk << 24 | m
+    sorted_ids = torch.full((max_padded,), init_val, dtype=torch.int32)
+    sorted_weights = torch.zeros((max_padded,), dtype=torch.float32)
+    sorted_expert_ids = torch.full((max_blocks,), -1, dtype=torch.int32)
+    num_valid = torch.empty((2,), dtype=torch.int32)
+    if num_local_tokens is not None:
+        topk_ids = topk_ids[: int(num_local_tokens.item())]
+    begin = 0
+    blk_begin = 0
+    skipped = 0
+    for e in range(num_experts):
+        if expert_mask is not None and int(expert_mask[e]) == 0:
+            skipped += 1
+            continue
+        token_id, slot_id = torch.where(topk_ids == e)
+        n = token_id.numel()
+        nblk = (n + block_size - 1) // block_size
+        sorted_ids[begin:begin + n] = (slot_id << 24 | token_id).to(torch.int32)
+        sorted_weights[begin:begin + n] = topk_weights[token_id, slot_id]
+        begin += nblk * block_size
+        sorted_expert_ids[blk_begin:blk_begin + nblk] = e - skipped
+        blk_begin += nblk
+    num_valid[0] = begin
+    num_valid[1] = topk_ids.shape[0]
+    return sorted_ids, sorted_weights, sorted_expert_ids, num_valid
+
+
+def local_expert_ids(topk_ids, expert_mask):
+    """aiter/fused_moe.py:3467-3470: local id = cumsum(mask) - 1, non-local -> -1."""
+    if expert_mask is None:
+        return topk_ids
+    mask = expert_mask.to(torch.int64)
+    local = torch.cumsum(mask, 0) - 1
+    local = torch.where(mask > 0, local, torch.full_like(local, -1))
+    return local[topk_ids.long()].to(topk_ids.dtype)
+
+
+# --------------------------------------------------------------------------- GEMM stages
+def _dequant_expert(w_q_e, w_s_e):
+    """aiter/fused_moe.py:3589-3594: w.view(N/128,128,K/128,128) * scale.view(N/128,1,K/128,1)."""
+    N, K = w_q_e.shape
+    w = w_q_e.to(torch.float32).view(N // 128, 128, K // 128, 128)
+    w = w * w_s_e.reshape(N // 128, 1, K // 128, 1)
+    return w.view(N, K)
+
+
+def moe_stage1_ref(a1_q, a1_scale, w1_q, w1_scale, topk_weight, topk_ids, inter_dim,
+                   dtype=torch.bfloat16, doweight=False):
+    """aiter/fused_moe.py:3532-3681, per_1x128/per_128x128 branch, g1u1, SiLU.
+
+    a1_q [M,H] e4m3 + a1_scale [M,H/128]; w1_q [E,2I,H] e4m3 + w1_scale
+    [E,2I/128,H/128]; topk_ids hold *local* expert ids (-1 = not on this rank).
+    Returns [M, topk, I] in ``dtype`` (rows of non-local routes are 0)."""
+    M, H = a1_q.shape
+    topk = topk_ids.shape[1]
+    E, N, _ = w1_q.shape
+    hidden = a1_q.to(torch.float32)
+    s = a1_scale.view(M, -1, 1).repeat(1, 1, H // a1_scale.view(M, -1).shape[1]).view(M, -1)
+    hidden = hidden * s
+    out = torch.zeros((M, topk, N), dtype=torch.float32)
+    for e in range(E):
+        mask = topk_ids == e
+        if mask.sum():
+            tok, _slot = torch.where(mask)
+            sub = hidden[tok]
+            w_e = _dequant_expert(w1_q[e], w1_scale[e])
+            act_in = sub @ w_e.transpose(0, 1)
+            if doweight:
+                act_in = act_in * topk_weight[mask].view(-1, 1)
+            out[mask] = act_in
+    if N == 2 * inter_dim:
+        gate, up = out.split([inter_dim, inter_dim], dim=-1)
+        out = F.silu(gate) * up
+    else:
+        out = F.silu(out)
+    return out.to(dtype)
+
+
+def moe_stage2_ref(a2_q, a2_scale, w2_q, w2_scale, topk_weight, topk_ids,
+                   dtype=torch.bfloat16, doweight=True):
+    """aiter/fused_moe.py:3684-3811, per_1x128/per_128x128 branch.
+
+    a2_q [M,topk,I] e4m3 + a2_scale [M,topk,I/128]; w2_q [E,H,I] + w2_scale
+    [E,H/128,I/128].  fp32 per-route results, times the route weight, summed
+    over top-k in fp32, one final cast."""
+    M, topk = topk_ids.shape
+    E, H, I = w2_q.shape
+    hidden = a2_q.to(torch.float32).view(M, topk, I)
+    s = a2_scale.view(M, topk, -1, 1).repeat(1, 1, 1, 128).view(M, topk, -1)
+    hidden = hidden * s
+    out = torch.zeros((M, topk, H), dtype=torch.float32)
+    for e in range(E):
+        mask = topk_ids == e
+        if mask.sum():
+            sub = hidden[mask]
+            w_e = _dequant_expert(w2_q[e], w2_scale[e])
+            out[mask] = sub @ w_e.transpose(0, 1)
+    if doweight:
+        out.mul_(topk_weight.view(M, -1, 1))
+    return out.sum(1).to(dtype)
+
+
+def fused_moe_ref(x, w1_q, w1_scale, w2_q, w2_scale, topk_weight, topk_ids,
+                  expert_mask=None, dtype=torch.bfloat16, return_stages=False,
+                  a1_q=None, a1_scale=None):
+    """The pipeline of op_tests/test_moe_2stage.py (per_128x128 branch):
+    a1 quant :237-242 -> torch_moe_stage1 :397-416 -> a2 quant :419-423 ->
+    torch_moe_stage2 :448-460.  ``expert_mask`` follows torch_moe
+    (aiter/fused_moe.py:3467-3470)."""
+    M, H = x.shape
+    I = w2_q.shape[2]
+    ids = local_expert_ids(topk_ids, expert_mask)
+    if a1_q is None:
+        a1_q, a1_scale = quant_1x128(x)
+    out1 = moe_stage1_ref(a1_q, a1_scale, w1_q, w1_scale, topk_weight, ids, I, dtype=dtype)
+    a2_q, a2_scale = quant_1x128(out1.view(-1, I))
+    topk = topk_ids.shape[1]
+    out = moe_stage2_ref(a2_q.view(M, topk, I), a2_scale.view(M, topk, -1), w2_q, w2_scale,
+                         topk_weight, ids, dtype=dtype)
+    if return_stages:
+        return out, dict(a1_q=a1_q, a1_scale=a1_scale, out1=out1,
+                         a2_q=a2_q.view(M, topk, I), a2_scale=a2_scale.view(M, topk, -1))
+    return out
+
+
+# --------------------------------------------------------------------------- routing
+def softmax_topk_ref(logits, topk, renormalize=True):
+    """aiter/fused_moe.py:4058-4129 (fused_topk): fp32 softmax, top-k, renormalise."""
+    scores = torch.softmax(logits.to(torch.float32), dim=-1)
+    w, ids = torch.topk(scores, k=topk, dim=-1)
+    if renormalize:
+        w = w / w.sum(dim=-1, keepdim=True)
+    return w.to(torch.float32), ids.to(torch.int32)
+
+
+def biased_grouped_topk_ref(gating, bias, topk, renormalize, num_expert_group, topk_group,
+                            routed_scaling_factor=1.0):
+    """aiter/ops/topk.py:217-259 (biased_grouped_topk_torch) followed by the
+    routed_scaling_factor multiply of the native op (aiter/ops/topk.py:90-99)."""
+    scores = gating.to(torch.float32).sigmoid()
+    n = scores.shape[0]
+    choice = scores.view(n, -1) + bias.unsqueeze(0)
+    group_scores = choice.view(n, num_expert_group, -1).topk(2, dim=-1)[0].sum(dim=-1)
+    group_idx = torch.topk(group_scores, k=topk_group, dim=-1, sorted=False)[1]
+    group_mask = torch.zeros_like(group_scores)
+    group_mask.scatter_(1, group_idx, 1)
+    score_mask = (group_mask.unsqueeze(-1)
+                  .expand(n, num_expert_group, scores.shape[-1] // num_expert_group)
+                  .reshape(n, -1))
+    tmp = choice.masked_fill(~score_mask.bool(), 0.0)
+    _, ids = torch.topk(tmp, k=topk, dim=-1, sorted=False)
+    w = scores.gather(1, ids)
+    if renormalize:
+        w = w / w.sum(dim=-1, keepdim=True)
+    w = w * routed_scaling_factor
+    return w.to(torch.float32), ids.to(torch.int32)
+
+
+# --------------------------------------------------------------------------- error metrics
+def error_stats(out: torch.Tensor, ref: torch.Tensor, atol=1e-2, rtol=1e-2):
+    """Parity statistics for a bf16 output against the oracle.
+
+    max_abs_over_rms: max |out-ref| / RMS(ref)   (bar: <= 0.02)
+    frac_within:      share of elements with |out-ref| <= atol + rtol*|ref|  (bar: >= 0.995)
+    n_diff / n_one_ulp: elements that differ at all / by exactly one bf16 ulp."""
+    o = out.detach().to("cpu", torch.float32)
+    r = ref.detach().to("cpu", torch.float32)
+    d = (o - r).abs()
+    rms = float(r.pow(2).mean().sqrt())
+    within = float((d <= atol + rtol * r.abs()).float().mean())
+    n_diff = int((d > 0).sum())
+    n_one_ulp = 0
+    if out.dtype == torch.bfloat16 and ref.dtype == torch.bfloat16:
+        ob = out.detach().cpu().view(torch.int16).to(torch.int32)
+        rb = ref.detach().cpu().view(torch.int16).to(torch.int32)
+        n_one_ulp = int(((ob - rb).abs() == 1).sum())
+    return dict(max_abs=float(d.max()), rms=rms,
+                max_abs_over_rms=float(d.max()) / max(rms, 1e-30),
+                frac_within=within, n_diff=n_diff, n_one_ulp=n_one_ulp,
+                numel=o.numel(), has_nan=bool(torch.isnan(o).any()))

@@ -1,0 +1,120 @@
+"""The CPU oracle against the fixtures written from the reference's own functions."""
+
+import numpy as np
+import torch
+
+from conftest import bits_equal, from_bits, load_golden
+from oracle import inputs, moe_oracle
+
+BF16 = torch.bfloat16
+FP8 = torch.float8_e4m3fn
+
+
+def test_sorting_known_answers():
+    g = load_golden("sorting_kat.npz")
+    ids = torch.from_numpy(g["topk_ids"])
+    w = torch.from_numpy(g["topk_weights"])
+    mask = torch.from_numpy(g["mask"])
+    for tag, m in (("plain", None), ("masked", mask)):
+        o = moe_oracle.moe_sorting_ref(ids, w, 6, 4, m, None)
+        assert np.array_equal(o[0].numpy(), g[f"{tag}_sorted_ids"])
+        assert np.array_equal(o[1].numpy(), g[f"{tag}_sorted_weights"])
+        assert np.array_equal(o[2].numpy(), g[f"{tag}_sorted_expert_ids"])
+        assert np.array_equal(o[3].numpy(), g[f"{tag}_num_valid"])
+    # figures written in the reference header's worked example
+    assert int(g["plain_num_valid"][0]) == 24
+    assert g["plain_sorted_expert_ids"][:6].tolist() == [0, 1, 2, 3, 3, 5]
+    assert int(g["masked_num_valid"][0]) == 20
+    assert g["masked_sorted_expert_ids"][:5].tolist() == [0, 1, 2, 2, 3]
+    local = moe_oracle.local_expert_ids(torch.from_numpy(g["ids3"]), torch.from_numpy(g["mask3"]))
+    assert local.tolist() == [[-1, 0, -1], [1, 2, -1], [-1, -1, 1]]
+
+
+def sorting_sweep_cases():
+    g = load_golden("sorting_sweep.npz")
+    keys = sorted(k[:-5] for k in g.files if k.endswith("_meta"))
+    for k in keys:
+        M, E, topk, B, _seed = g[k + "_meta"].tolist()
+        ids = torch.from_numpy(g[k + "_ids"])
+        w = torch.from_numpy(g[k + "_w"])
+        mask = torch.from_numpy(g[k + "_mask"]) if k + "_mask" in g.files else None
+        nl = torch.from_numpy(g[k + "_nl"]) if k + "_nl" in g.files else None
+        exp = tuple(torch.from_numpy(g[k + s]) for s in
+                    ("_sorted_ids", "_sorted_weights", "_sorted_expert_ids", "_num_valid"))
+        yield k, (ids, w, E, B, mask, nl), exp
+
+
+def test_sorting_sweep():
+    n = 0
+    for k, args, exp in sorting_sweep_cases():
+        o = moe_oracle.moe_sorting_ref(*args)
+        for a, b in zip(o, exp):
+            assert bits_equal(a, b), k
+        n += 1
+    assert n == 21
+
+
+def test_quant_1x128():
+    g = load_golden("quant_1x128.npz")
+    x = from_bits(g["x"], BF16)
+    q, s = moe_oracle.quant_1x128(x)
+    assert np.array_equal(q.view(torch.uint8).numpy(), g["q"])
+    assert np.array_equal(s.numpy(), g["scale"])
+    assert float(s[0, 0]) == 1.0  # all-zero group
+
+
+def _check_layer(name, fname):
+    g = load_golden(fname)
+    c = inputs.make_config(name, seed=0)
+    # the seeded inputs are the ones the fixture was made from
+    assert np.array_equal(c["topk_ids"].numpy(), g["topk_ids"])
+    assert np.array_equal(c["w1_scale"].numpy(), g["w1_scale"])
+    assert int(c["w1_q"].view(torch.uint8).long().sum()) == int(g["w1_q_sum"])
+    out, st = moe_oracle.fused_moe_ref(c["x"], c["w1_q"], c["w1_scale"], c["w2_q"], c["w2_scale"],
+                                       c["topk_weight"], c["topk_ids"], return_stages=True)
+    assert np.array_equal(st["a1_q"].view(torch.uint8).numpy(), g["a1_q"])
+    assert np.array_equal(st["a1_scale"].numpy(), g["a1_scale"])
+    # fp32 sgemm blocking may depend on the host's thread count: allow isolated 1-ulp flips
+    ref1 = from_bits(g["out1"], BF16)
+    s1 = moe_oracle.error_stats(st["out1"], ref1)
+    assert s1["n_diff"] == s1["n_one_ulp"] and s1["n_diff"] <= 2e-3 * s1["numel"], s1
+    ref = from_bits(g["out"], BF16)
+    s2 = moe_oracle.error_stats(out, ref)
+    assert s2["max_abs_over_rms"] <= 0.02 and s2["frac_within"] >= 0.999, s2
+
+
+def test_layer_cfg0():
+    _check_layer("cfg0", "cfg0.npz")
+
+
+def test_layer_dsv3_slice():
+    _check_layer("dsv3_slice", "dsv3_slice.npz")
+
+
+def test_expert_parallel_partials_sum():
+    g = load_golden("cfg0_ep2.npz")
+    g0 = load_golden("cfg0.npz")
+    c = inputs.make_config("cfg0", seed=0)
+    E = c["cfg"]["E"]
+    total = torch.zeros((c["cfg"]["M"], c["cfg"]["H"]))
+    for rank in range(2):
+        m = torch.from_numpy(g[f"mask{rank}"])
+        sl = slice(rank * E // 2, (rank + 1) * E // 2)
+        o = moe_oracle.fused_moe_ref(c["x"], c["w1_q"][sl], c["w1_scale"][sl], c["w2_q"][sl],
+                                     c["w2_scale"][sl], c["topk_weight"], c["topk_ids"], expert_mask=m)
+        s = moe_oracle.error_stats(o, from_bits(g[f"out{rank}"], BF16))
+        assert s["max_abs_over_rms"] <= 0.02 and s["frac_within"] >= 0.999, s
+        total += o.float()
+    s = moe_oracle.error_stats(total.to(BF16), from_bits(g0["out"], BF16))
+    assert s["max_abs_over_rms"] <= 0.03 and s["frac_within"] >= 0.995, s
+
+
+def test_routing_dsv3():
+    g = load_golden("routing_dsv3.npz")
+    w, ids = moe_oracle.biased_grouped_topk_ref(torch.from_numpy(g["logits"]), torch.from_numpy(g["bias"]),
+                                                8, True, 8, 4, 2.5)
+    assert np.array_equal(ids.numpy(), g["ids"])
+    assert np.array_equal(w.numpy(), g["weights"])
+    # every token: 8 distinct experts from at most 4 groups of 32
+    assert all(len(set(r.tolist())) == 8 for r in ids)
+    assert all(len(set((r // 32).tolist())) <= 4 for r in ids)
