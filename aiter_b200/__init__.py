@@ -1,0 +1,21 @@
+"""aiter_b200: the FP8 block-scaled fused-MoE path of ROCm/aiter, rebuilt for NVIDIA B200.
+
+Public surface (same names as the reference's): ``fused_moe``, ``moe_sorting``, ``QuantType``,
+``ActivationType``, ``dtypes``, ``get_hip_quant`` / ``per_group_quant_hip``.
+"""
+
+from . import dtypes  # noqa: F401
+from .enums import ActivationType, QuantType  # noqa: F401
+from .fused_moe import (  # noqa: F401
+    check_device_status,
+    fused_moe,
+    get_hip_quant,
+    moe_sorting,
+    moe_sorting_get_workspace_size,
+    per_group_quant_hip,
+)
+
+__all__ = [
+    "ActivationType", "QuantType", "dtypes", "fused_moe", "moe_sorting",
+    "moe_sorting_get_workspace_size", "get_hip_quant", "per_group_quant_hip", "check_device_status",
+]

@@ -1,0 +1,146 @@
+// C-ABI entry points of libaiter_b200.so (declared in include/aiter_b200.h) and the error bridge.
+// Conventions of the reference's ctypes FFI: int status, thread-local last-error string, stream as
+// the last argument (csrc/include/aiter_ctypes_error.h:55-155, aiter/jit/core.py:1306-1620).
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace b200 {
+
+std::string& last_error() {
+    static thread_local std::string msg;
+    return msg;
+}
+
+int64_t sorting_workspace_bytes(int tokens, int num_experts, int topk);
+void launch_moe_sorting(const aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*,
+                        aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*, int, int, const aiter_tensor_t*,
+                        const aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*, cudaStream_t);
+void launch_quant_1x128(aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*, cudaStream_t);
+void launch_moe_stage1(const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*,
+                       const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*,
+                       aiter_tensor_t*, aiter_tensor_t*, cudaStream_t);
+void launch_moe_stage2(const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*,
+                       const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*,
+                       aiter_tensor_t*, aiter_tensor_t*, cudaStream_t);
+
+namespace {
+
+// out = RNE(acc): 8 fp32 in, 8 half-precision values out per thread.
+template <typename T2>
+__global__ void __launch_bounds__(256) finalize_kernel(const float4* __restrict__ acc, uint4* __restrict__ out,
+                                                       int64_t n8) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (int64_t)gridDim.x * blockDim.x) {
+        const float4 a = __ldcs(acc + 2 * i), b = __ldcs(acc + 2 * i + 1);
+        uint4 o;
+        if constexpr (sizeof(T2) == sizeof(__nv_bfloat162) && std::is_same<T2, __nv_bfloat162>::value) {
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(a.x, a.y), p1 = __floats2bfloat162_rn(a.z, a.w);
+            __nv_bfloat162 p2 = __floats2bfloat162_rn(b.x, b.y), p3 = __floats2bfloat162_rn(b.z, b.w);
+            o = make_uint4(*(uint32_t*)&p0, *(uint32_t*)&p1, *(uint32_t*)&p2, *(uint32_t*)&p3);
+        } else {
+            __half2 p0 = __floats2half2_rn(a.x, a.y), p1 = __floats2half2_rn(a.z, a.w);
+            __half2 p2 = __floats2half2_rn(b.x, b.y), p3 = __floats2half2_rn(b.z, b.w);
+            o = make_uint4(*(uint32_t*)&p0, *(uint32_t*)&p1, *(uint32_t*)&p2, *(uint32_t*)&p3);
+        }
+        out[i] = o;
+    }
+}
+
+void launch_finalize(aiter_tensor_t* out, const aiter_tensor_t* acc, cudaStream_t stream) {
+    check_tensor(acc, "acc", AITER_DTYPE_fp32, -1);
+    check_tensor(out, "out", -1, -1);
+    B200_CHECK(out->dtype_ == AITER_DTYPE_bf16 || out->dtype_ == AITER_DTYPE_fp16,
+               "out must be bf16 or fp16");
+    B200_CHECK(out->numel_ == acc->numel_, "out and acc must have the same number of elements");
+    B200_CHECK(acc->numel_ % 8 == 0, "element count must be a multiple of 8");
+    B200_CHECK(((uintptr_t)acc->ptr & 15) == 0 && ((uintptr_t)out->ptr & 15) == 0, "buffers must be 16-byte aligned");
+    const int64_t n8 = (int64_t)acc->numel_ / 8;
+    if (n8 == 0) return;
+    int64_t blocks = (n8 + 255) / 256;
+    const int64_t cap = (int64_t)sm_count(acc->device_id) * 8;
+    if (blocks > cap) blocks = cap;
+    if (out->dtype_ == AITER_DTYPE_bf16)
+        finalize_kernel<__nv_bfloat162><<<(unsigned)blocks, 256, 0, stream>>>((const float4*)acc->ptr, (uint4*)out->ptr, n8);
+    else
+        finalize_kernel<__half2><<<(unsigned)blocks, 256, 0, stream>>>((const float4*)acc->ptr, (uint4*)out->ptr, n8);
+    B200_CUDA(cudaGetLastError());
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+#define B200_EXPORT __attribute__((visibility("default")))
+
+extern "C" {
+
+B200_EXPORT int aiter_ctypes_abi_version(void) { return 2; }
+
+B200_EXPORT const char* aiter_get_last_error(void) { return last_error().empty() ? nullptr : last_error().c_str(); }
+
+B200_EXPORT void aiter_clear_last_error(void) { last_error().clear(); }
+
+B200_EXPORT int64_t b200_moe_sorting_get_workspace_size(int tokens, int num_experts, int topk) {
+    return sorting_workspace_bytes(tokens, num_experts, topk);
+}
+
+B200_EXPORT int b200_moe_sorting_fwd(const aiter_tensor_t* topk_ids, const aiter_tensor_t* topk_weights,
+                         aiter_tensor_t* sorted_token_ids, aiter_tensor_t* sorted_weights,
+                         aiter_tensor_t* sorted_expert_ids, aiter_tensor_t* num_valid_ids, aiter_tensor_t* moe_buf,
+                         int num_experts, int unit_size, const aiter_tensor_t* local_expert_mask,
+                         const aiter_tensor_t* num_local_tokens, aiter_tensor_t* workspace, int dispatch_policy,
+                         aiter_tensor_t* local_topk_ids, void* stream) {
+    (void)dispatch_policy;  // the reference's one-shot / multi-phase choice; made from the sizes here
+    return safe_call([&] {
+        B200_CHECK(topk_ids != nullptr, "topk_ids must not be NULL");
+        DeviceGuard g(topk_ids->device_id);
+        launch_moe_sorting(topk_ids, topk_weights, sorted_token_ids, sorted_weights, sorted_expert_ids,
+                           num_valid_ids, moe_buf, num_experts, unit_size, local_expert_mask, num_local_tokens,
+                           workspace, local_topk_ids, (cudaStream_t)stream);
+    });
+}
+
+B200_EXPORT int b200_moe_quant_1x128(aiter_tensor_t* out, const aiter_tensor_t* input, aiter_tensor_t* scales, void* stream) {
+    return safe_call([&] {
+        B200_CHECK(input != nullptr, "input must not be NULL");
+        DeviceGuard g(input->device_id);
+        launch_quant_1x128(out, input, scales, (cudaStream_t)stream);
+    });
+}
+
+B200_EXPORT int b200_moe_stage1(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale, const aiter_tensor_t* w1,
+                    const aiter_tensor_t* w1_scale, const aiter_tensor_t* sorted_token_ids,
+                    const aiter_tensor_t* sorted_expert_ids, const aiter_tensor_t* num_valid_ids, aiter_tensor_t* a2,
+                    aiter_tensor_t* a2_scale, aiter_tensor_t* status, void* stream) {
+    return safe_call([&] {
+        B200_CHECK(a1 != nullptr, "a1 must not be NULL");
+        DeviceGuard g(a1->device_id);
+        launch_moe_stage1(a1, a1_scale, w1, w1_scale, sorted_token_ids, sorted_expert_ids, num_valid_ids, a2,
+                          a2_scale, status, (cudaStream_t)stream);
+    });
+}
+
+B200_EXPORT int b200_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* a2_scale, const aiter_tensor_t* w2,
+                    const aiter_tensor_t* w2_scale, const aiter_tensor_t* sorted_token_ids,
+                    const aiter_tensor_t* sorted_weights, const aiter_tensor_t* sorted_expert_ids,
+                    const aiter_tensor_t* num_valid_ids, aiter_tensor_t* acc, aiter_tensor_t* status, void* stream) {
+    return safe_call([&] {
+        B200_CHECK(a2 != nullptr, "a2 must not be NULL");
+        DeviceGuard g(a2->device_id);
+        launch_moe_stage2(a2, a2_scale, w2, w2_scale, sorted_token_ids, sorted_weights, sorted_expert_ids,
+                          num_valid_ids, acc, status, (cudaStream_t)stream);
+    });
+}
+
+B200_EXPORT int b200_moe_finalize(aiter_tensor_t* out, const aiter_tensor_t* acc, void* stream) {
+    return safe_call([&] {
+        B200_CHECK(acc != nullptr, "acc must not be NULL");
+        DeviceGuard g(acc->device_id);
+        launch_finalize(out, acc, (cudaStream_t)stream);
+    });
+}
+
+}  // extern "C"

@@ -1,0 +1,506 @@
+// Grouped FP8 block-scaled GEMMs of the fused-MoE layer for sm_100a (tcgen05 + TMEM + TMA).
+//
+//   stage 1: for every sorted 128-row block (one expert):  [gate|up] = A1 . W1_e^T, then
+//            SiLU(gate)*up -> bf16 rounding -> 1x128 FP8 requantisation, written in sorted order
+//   stage 2: [128 x 256] = A2 . W2_e^T, times the route weight, added into fp32 acc[token]
+//
+// Replaces the reference's CK DeviceMoeGemmBlockScale instances
+// (csrc/ck_gemm_moe_2stages_codegen/gemm_moe_ck2stages_common_blockscale.cuh:25-169,335-466)
+// and follows the arithmetic of its torch oracle (aiter/fused_moe.py:3532-3811).
+//
+// One persistent CTA per SM walks tiles (block, n-tile) = (t / n_tiles, t % n_tiles), t = blockIdx.x,
+// blockIdx.x + gridDim.x, ...; the tile count comes from num_valid_ids on the device (no host sync).
+// Per tile and per 128-wide K block:
+//   warp 0      TMA-loads two [128 rows x 128 B] weight boxes (gate+up rows, or 256 output rows)
+//               into a 128B-swizzled shared-memory stage;
+//   warps 4-7   gather the 128 activation rows of the block (cp.async, 16 B chunks, same swizzle);
+//   warp 1      issues 4 tcgen05.mma (M128 N256 K32, e4m3 -> fp32) into one of two 256-column
+//               TMEM stages, then commits to free the smem stage and to publish the TMEM stage;
+//   warps 8-15  read the TMEM stage (tcgen05.ld) and fold it into fp32 registers with the block
+//               scales:  acc += partial * (a_scale[row, kb] * w_scale[e, nblk, kb]).
+// The scales are fp32 per 128-K block (not UE8M0 per 32), so the hardware block-scaled MMA kinds do
+// not apply; the per-K-block promotion runs on the CUDA cores and overlaps the next block's MMAs.
+// After the last K block the same warps run the stage's epilogue from registers.
+//
+// All mbarrier waits are bounded (sm100_ptx.cuh); if one runs out, status[0] is set and the kernel
+// winds down: every role leaves its loops, the CTA meets at the tail and frees its TMEM.
+
+#include <cuda_fp8.h>
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int BM = 128;            // sorted rows per tile (== sort unit)
+constexpr int BK = 128;            // K elements (bytes) per pipeline step == scale block
+constexpr int BN = 256;            // UMMA N: 128 gate + 128 up columns, or 256 output columns
+constexpr int kStages = 4;         // shared-memory pipeline depth
+constexpr int kLag = 2;            // cp.async groups a gather thread keeps in flight
+constexpr int kABytes = BM * BK;   // 16 KB
+constexpr int kBBytes = BN * BK;   // 32 KB
+constexpr int kThreads = 512;
+constexpr int kGatherWarp0 = 4;    // warps 4..7
+constexpr int kEpiWarp0 = 8;       // warps 8..15
+constexpr int kEpiThreads = 256;
+constexpr int kTmemCols = 512;     // 2 stages x 256 fp32 columns
+constexpr uint32_t kIdesc = ptx::make_idesc_e4m3_f32(BM, BN);
+
+// shared memory map (offsets from a 1024-byte aligned base)
+constexpr int kOffA = 0;
+constexpr int kOffB = kOffA + kStages * kABytes;
+constexpr int kOffBar = kOffB + kStages * kBBytes;          // mbarriers (8 B each)
+constexpr int kNumBars = 2 * kStages + 4;
+constexpr int kOffTmemSlot = kOffBar + kNumBars * 8;
+constexpr int kOffAbort = kOffTmemSlot + 4;
+constexpr int kOffAmax = (kOffAbort + 4 + 15) & ~15;        // float [2 tiles][2 halves][128 rows]
+constexpr int kSmemUsed = kOffAmax + 2 * 2 * BM * 4;
+constexpr int kSmemBytes = kSmemUsed + 1024;                // slack for the 1024-byte alignment
+
+struct GemmParams {
+    const uint8_t* a;        // stage 1: a1 [M,K] by token; stage 2: a2 [P,K] by sorted row
+    const float* a_scale;    // [rows, K/128]
+    const float* w_scale;    // [E, n_rows/128, K/128]
+    const int* sorted_ids;
+    const float* sorted_w;
+    const int* sorted_eids;
+    const int* num_valid;    // {padded total, tokens}
+    int M;                   // static token count
+    int K, KB;               // K and K/128
+    int n_tiles;             // stage 1: I/128; stage 2: ceil(H/256)
+    int n_rows;              // weight rows per expert: 2I (stage 1) or H (stage 2)
+    int inter;               // I
+    uint8_t* a2;             // stage 1 out [P, I] fp8
+    float* a2_scale;         // stage 1 out [P, I/128]
+    float* acc;              // stage 2 out [M, H] fp32
+    int* status;
+};
+
+__device__ __forceinline__ float silu_mul(float g, float u) {
+    // torch: silu(x) = x / (1 + exp(-x)) in fp32, then * up (aiter/fused_moe.py:3676)
+    return __fdiv_rn(g, 1.0f + expf(-g)) * u;
+}
+
+template <int STAGE>
+__global__ void __launch_bounds__(kThreads, 1)
+moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const uint32_t sbase = ptx::smem_u32(smem);
+    const uint32_t sA = sbase + kOffA, sB = sbase + kOffB;
+    const uint32_t bar0 = sbase + kOffBar;
+    auto full_bar = [&](int s) { return bar0 + 8u * s; };
+    auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
+    auto tfull_bar = [&](int s) { return bar0 + 8u * (2 * kStages + s); };
+    auto tempty_bar = [&](int s) { return bar0 + 8u * (2 * kStages + 2 + s); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kOffTmemSlot);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffAbort);
+    float* amax_x = reinterpret_cast<float*>(smem + kOffAmax);
+
+    const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            ptx::mbar_init(full_bar(s), BM + 1);   // 128 gather threads + the TMA thread
+            ptx::mbar_init(empty_bar(s), 1);       // one tcgen05.commit
+        }
+        for (int s = 0; s < 2; ++s) {
+            ptx::mbar_init(tfull_bar(s), 1);                 // one tcgen05.commit
+            ptx::mbar_init(tempty_bar(s), kEpiThreads / 32); // one arrive per epilogue warp
+        }
+        *abort_flag = 0;
+        ptx::fence_mbar_init();
+        ptx::prefetch_tensormap(&tmap_w);
+    }
+    if (warp == 2) {
+        ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int num_valid = p.num_valid[0];
+    const int tokens = min(p.num_valid[1], p.M);
+    const int total_tiles = (num_valid / BM) * p.n_tiles;
+
+    if (warp < kGatherWarp0) {
+        ptx::setmaxnreg_dec<48>();
+        if (warp == 0 && lane == 0) {
+            // ---------------------------------------------------------------- weight TMA producer
+            uint32_t it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+                const int blk = t / p.n_tiles, nt = t - blk * p.n_tiles;
+                const int e = p.sorted_eids[blk];
+                int r0, r1;
+                if (STAGE == 1) {
+                    r0 = e * p.n_rows + nt * 128;   // gate rows
+                    r1 = r0 + p.inter;              // up rows
+                } else {
+                    r0 = e * p.n_rows + nt * 256;
+                    r1 = (nt * 256 + 128 < p.n_rows) ? r0 + 128 : r0;
+                }
+                for (int kb = 0; kb < p.KB; ++kb, ++it) {
+                    const int s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1u;
+                    if (!(ok = ptx::mbar_wait(empty_bar(s), ph ^ 1u, abort_flag))) break;
+                    ptx::mbar_arrive_expect_tx(full_bar(s), kBBytes);
+                    ptx::tma_load_2d(sB + s * kBBytes, &tmap_w, kb * BK, r0, full_bar(s));
+                    ptx::tma_load_2d(sB + s * kBBytes + kBBytes / 2, &tmap_w, kb * BK, r1, full_bar(s));
+                }
+            }
+        } else if (warp == 1 && lane == 0) {
+            // ---------------------------------------------------------------- UMMA issuer
+            uint32_t it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+                for (int kb = 0; kb < p.KB; ++kb, ++it) {
+                    const int s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1u;
+                    const int ts = it & 1;
+                    const uint32_t tph = (it >> 1) & 1u;
+                    if (!(ok = ptx::mbar_wait(tempty_bar(ts), tph ^ 1u, abort_flag))) break;
+                    if (!(ok = ptx::mbar_wait(full_bar(s), ph, abort_flag))) break;
+                    ptx::tc_fence_after();
+                    const uint64_t da = ptx::make_kmajor_sw128_desc(sA + s * kABytes);
+                    const uint64_t db = ptx::make_kmajor_sw128_desc(sB + s * kBBytes);
+                    const uint32_t d = tmem_base + ts * BN;
+#pragma unroll
+                    for (int k = 0; k < BK / 32; ++k)   // 32 bytes of K per UMMA: +2 in 16-byte units
+                        ptx::umma_f8(d, da + 2u * k, db + 2u * k, kIdesc, k > 0 ? 1u : 0u);
+                    ptx::umma_commit(empty_bar(s));
+                    ptx::umma_commit(tfull_bar(ts));
+                }
+            }
+        }
+    } else if (warp < kEpiWarp0) {
+        // -------------------------------------------------------------------- activation gather
+        ptx::setmaxnreg_dec<48>();
+        const int r = threadIdx.x - kGatherWarp0 * 32;   // row of the tile
+        const uint32_t sw = (uint32_t)(r & 7);
+        uint32_t it = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+            const int blk = t / p.n_tiles;
+            const int prow = blk * BM + r;
+            const uint8_t* src;
+            uint32_t nbytes = 16;
+            if (STAGE == 1) {
+                const int tok = p.sorted_ids[prow] & 0xFFFFFF;
+                const bool valid = tok < tokens;
+                src = p.a + (size_t)(valid ? tok : 0) * p.K;
+                nbytes = valid ? 16u : 0u;   // pads: zero-filled rows
+            } else {
+                src = p.a + (size_t)prow * p.K;
+            }
+            for (int kb = 0; kb < p.KB; ++kb, ++it) {
+                const int s = it % kStages;
+                const uint32_t ph = (it / kStages) & 1u;
+                if (!(ok = ptx::mbar_wait(empty_bar(s), ph ^ 1u, abort_flag))) break;
+                const uint32_t dst = sA + s * kABytes + r * BK;
+                const uint8_t* g = src + (size_t)kb * BK;
+#pragma unroll
+                for (uint32_t c = 0; c < 8; ++c) ptx::cp_async16(dst + ((c ^ sw) << 4), g + c * 16, nbytes);
+                ptx::cp_async_commit();
+                if (it >= (uint32_t)kLag) {
+                    ptx::cp_async_wait<kLag>();
+                    ptx::fence_proxy_async();
+                    ptx::mbar_arrive(full_bar((it - kLag) % kStages));
+                }
+            }
+        }
+        // drain: the last kLag steps still owe their arrival
+        ptx::cp_async_wait<0>();
+        ptx::fence_proxy_async();
+        if (ok) {
+            for (uint32_t j = (it > (uint32_t)kLag ? it - kLag : 0u); j < it; ++j)
+                ptx::mbar_arrive(full_bar(j % kStages));
+        }
+    } else {
+        // -------------------------------------------------------------------- promotion + epilogue
+        ptx::setmaxnreg_inc<208>();
+        const int q = warp & 3;                         // TMEM lane quarter this warp may read
+        const int half = (warp - kEpiWarp0) >> 2;       // which 64 columns of each 128-column group
+        const int r = q * 32 + lane;                    // row of the tile == TMEM lane
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
+        uint32_t it = 0;
+        uint32_t tile_par = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, tile_par ^= 1u) {
+            const int blk = t / p.n_tiles, nt = t - blk * p.n_tiles;
+            const int e = p.sorted_eids[blk];
+            const int prow = blk * BM + r;
+            const int tok = p.sorted_ids[prow] & 0xFFFFFF;
+            const bool valid = tok < tokens;
+            const float* as_row;
+            int nb0, nb1;
+            if (STAGE == 1) {
+                as_row = p.a_scale + (size_t)(valid ? tok : 0) * p.KB;
+                nb0 = nt;
+                nb1 = p.inter / 128 + nt;
+            } else {
+                as_row = p.a_scale + (size_t)prow * p.KB;
+                nb0 = nt * 2;
+                nb1 = min(nt * 2 + 1, p.n_rows / 128 - 1);
+            }
+            const float* ws0 = p.w_scale + ((size_t)e * (p.n_rows / 128) + nb0) * p.KB;
+            const float* ws1 = p.w_scale + ((size_t)e * (p.n_rows / 128) + nb1) * p.KB;
+
+            float acc[128];
+#pragma unroll
+            for (int j = 0; j < 128; ++j) acc[j] = 0.f;
+
+            for (int kb = 0; kb < p.KB; ++kb, ++it) {
+                const int ts = it & 1;
+                const uint32_t tph = (it >> 1) & 1u;
+                const float sa = (STAGE == 2 || valid) ? __ldg(as_row + kb) : 0.f;
+                const float s0 = sa * __ldg(ws0 + kb);
+                const float s1 = sa * __ldg(ws1 + kb);
+                if (!(ok = ptx::mbar_wait(tfull_bar(ts), tph, abort_flag))) break;
+                ptx::tc_fence_after();
+                const uint32_t ta = lane_addr + ts * BN + half * 64;
+                uint32_t v[64];
+                ptx::tmem_ld_x32(ta, v);
+                ptx::tmem_ld_x32(ta + 32, v + 32);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 64; ++j) acc[j] = fmaf(__uint_as_float(v[j]), s0, acc[j]);
+                ptx::tmem_ld_x32(ta + 128, v);
+                ptx::tmem_ld_x32(ta + 160, v + 32);
+                ptx::tmem_ld_wait();
+                // all reads of this TMEM stage are done: hand it back to the MMA warp
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(tempty_bar(ts));
+#pragma unroll
+                for (int j = 0; j < 64; ++j) acc[64 + j] = fmaf(__uint_as_float(v[j]), s1, acc[64 + j]);
+            }
+            if (!ok) break;
+
+            if (STAGE == 1) {
+                // SiLU(gate)*up in fp32 -> bf16 (RNE) -> 1x128 requant, as the oracle does:
+                // aiter/fused_moe.py:3668-3681 then aiter/ops/quant.py:64-94 on the bf16 values.
+                float amax = 0.f;
+#pragma unroll
+                for (int j = 0; j < 64; ++j) {
+                    float h = __bfloat162float(__float2bfloat16_rn(silu_mul(acc[j], acc[64 + j])));
+                    acc[j] = h;
+                    amax = fmaxf(amax, fabsf(h));
+                }
+                float* ax = amax_x + tile_par * (2 * BM);
+                ax[half * BM + r] = amax;
+                ptx::named_barrier(1, kEpiThreads);
+                amax = fmaxf(amax, ax[(half ^ 1) * BM + r]);
+                float scale = __fdiv_rn(amax, 448.0f);
+                if (scale == 0.f) scale = 1.f;
+                uint32_t w[16];
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    float2 lo = make_float2(__fdiv_rn(acc[4 * j], scale), __fdiv_rn(acc[4 * j + 1], scale));
+                    float2 hi = make_float2(__fdiv_rn(acc[4 * j + 2], scale), __fdiv_rn(acc[4 * j + 3], scale));
+                    uint32_t a = __nv_cvt_float2_to_fp8x2(lo, __NV_SATFINITE, __NV_E4M3);
+                    uint32_t b = __nv_cvt_float2_to_fp8x2(hi, __NV_SATFINITE, __NV_E4M3);
+                    w[j] = a | (b << 16);
+                }
+                uint4* dst = reinterpret_cast<uint4*>(p.a2 + (size_t)prow * p.inter + nt * 128 + half * 64);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) dst[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+                if (half == 0) p.a2_scale[(size_t)prow * (p.inter / 128) + nt] = scale;
+            } else {
+                // out[token] += weight * row  (aiter/fused_moe.py:3802-3811); fp32 L2 reductions
+                if (valid) {
+                    const float wgt = p.sorted_w[prow];
+                    const int H = p.n_rows;
+                    float* dst = p.acc + (size_t)tok * H + nt * 256 + half * 64;
+#pragma unroll
+                    for (int j = 0; j < 64; j += 4)
+                        ptx::red_add_v4(dst + j, wgt * acc[j], wgt * acc[j + 1], wgt * acc[j + 2], wgt * acc[j + 3]);
+                    if (nt * 256 + 128 < H) {
+#pragma unroll
+                        for (int j = 0; j < 64; j += 4)
+                            ptx::red_add_v4(dst + 128 + j, wgt * acc[64 + j], wgt * acc[65 + j],
+                                            wgt * acc[66 + j], wgt * acc[67 + j]);
+                    }
+                }
+            }
+        }
+    }
+
+    // ------------------------------------------------------------------------ tail
+    if (*abort_flag) {
+        if (threadIdx.x == 0) atomicExch(p.status, 1);
+        // give copies / MMAs still in flight a bounded time to land before TMEM is released
+        const long long t0 = clock64();
+        while (clock64() - t0 < 2000000LL) {
+        }
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------------------------- host
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        B200_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres));
+        B200_CHECK(sym != nullptr && qres == cudaDriverEntryPointSuccess,
+                   "cuTensorMapEncodeTiled is not available in this driver");
+        fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+// 2-D view [rows, K] of an fp8 weight tensor [E, n_rows, K]; boxes of 128 rows x 128 bytes, 128B swizzle.
+CUtensorMap make_weight_map(const void* ptr, uint64_t rows, uint64_t K) {
+    CUtensorMap m;
+    cuuint64_t dims[2] = {K, rows};
+    cuuint64_t strides[1] = {K};
+    cuuint32_t box[2] = {128, 128};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode_tiled_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides,
+                                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    B200_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", (int)r);
+    return m;
+}
+
+template <int STAGE>
+void launch_gemm(const CUtensorMap& tmap, const GemmParams& p, int64_t max_tiles, int dev, cudaStream_t stream) {
+    static bool attr_set[64] = {false};
+    if (dev >= 64 || !attr_set[dev]) {
+        B200_CUDA(cudaFuncSetAttribute(moe_gemm_kernel<STAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kSmemBytes));
+        if (dev < 64) attr_set[dev] = true;
+    }
+    int64_t grid = sm_count(dev);
+    if (max_tiles < grid) grid = max_tiles;
+    if (grid < 1) return;
+    moe_gemm_kernel<STAGE><<<(unsigned)grid, kThreads, kSmemBytes, stream>>>(tmap, p);
+    B200_CUDA(cudaGetLastError());
+}
+
+}  // namespace
+
+void launch_moe_stage1(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale, const aiter_tensor_t* w1,
+                       const aiter_tensor_t* w1_scale, const aiter_tensor_t* sorted_ids,
+                       const aiter_tensor_t* sorted_eids, const aiter_tensor_t* num_valid, aiter_tensor_t* a2,
+                       aiter_tensor_t* a2_scale, aiter_tensor_t* status, cudaStream_t stream) {
+    check_tensor(a1, "a1", AITER_DTYPE_fp8, 2);
+    check_tensor(a1_scale, "a1_scale", AITER_DTYPE_fp32, -1);
+    check_tensor(w1, "w1", AITER_DTYPE_fp8, 3);
+    check_tensor(w1_scale, "w1_scale", AITER_DTYPE_fp32, -1);
+    check_tensor(sorted_ids, "sorted_token_ids", AITER_DTYPE_i32, 1);
+    check_tensor(sorted_eids, "sorted_expert_ids", AITER_DTYPE_i32, 1);
+    check_tensor(num_valid, "num_valid_ids", AITER_DTYPE_i32, 1);
+    check_tensor(a2, "a2", AITER_DTYPE_fp8, 2);
+    check_tensor(a2_scale, "a2_scale", AITER_DTYPE_fp32, -1);
+    check_tensor(status, "status", AITER_DTYPE_i32, -1);
+    const int64_t M = a1->shape[0], H = a1->shape[1];
+    const int64_t E = w1->shape[0], N2 = w1->shape[1];
+    B200_CHECK(w1->shape[2] == H, "w1 must be [E, 2*inter_dim, model_dim]: K ", w1->shape[2], " != ", H);
+    B200_CHECK(N2 % 256 == 0, "2*inter_dim must be a multiple of 256 (inter_dim % 128 == 0), got ", N2);
+    B200_CHECK(H % 128 == 0, "model_dim must be a multiple of 128, got ", H);
+    const int64_t I = N2 / 2;
+    B200_CHECK((int64_t)a1_scale->numel_ == M * (H / 128), "a1_scale must have M*model_dim/128 elements");
+    B200_CHECK((int64_t)w1_scale->numel_ == E * (N2 / 128) * (H / 128),
+               "w1_scale must have E*(2*inter_dim/128)*(model_dim/128) elements");
+    const int64_t P = a2->shape[0];
+    B200_CHECK(a2->shape[1] == I, "a2 must be [P, inter_dim]");
+    B200_CHECK((int64_t)sorted_ids->numel_ >= 1 && P >= (int64_t)sorted_ids->numel_,
+               "a2 must have at least as many rows as sorted_token_ids (", sorted_ids->numel_, "), has ", P);
+    B200_CHECK((int64_t)a2_scale->numel_ >= P * (I / 128), "a2_scale must have P*inter_dim/128 elements");
+    B200_CHECK(num_valid->numel_ >= 2 && status->numel_ >= 1, "num_valid_ids needs 2 and status 1 element");
+    B200_CHECK(E * N2 < ((int64_t)1 << 31) && M < (1 << 24), "problem too large");
+    B200_CHECK(((uintptr_t)a1->ptr & 15) == 0 && ((uintptr_t)w1->ptr & 15) == 0 && ((uintptr_t)a2->ptr & 15) == 0,
+               "a1, w1 and a2 must be 16-byte aligned");
+
+    GemmParams p{};
+    p.a = (const uint8_t*)a1->ptr;
+    p.a_scale = (const float*)a1_scale->ptr;
+    p.w_scale = (const float*)w1_scale->ptr;
+    p.sorted_ids = (const int*)sorted_ids->ptr;
+    p.sorted_eids = (const int*)sorted_eids->ptr;
+    p.num_valid = (const int*)num_valid->ptr;
+    p.M = (int)M;
+    p.K = (int)H;
+    p.KB = (int)(H / 128);
+    p.n_tiles = (int)(I / 128);
+    p.n_rows = (int)N2;
+    p.inter = (int)I;
+    p.a2 = (uint8_t*)a2->ptr;
+    p.a2_scale = (float*)a2_scale->ptr;
+    p.status = (int*)status->ptr;
+    CUtensorMap tmap = make_weight_map(w1->ptr, (uint64_t)(E * N2), (uint64_t)H);
+    const int64_t max_tiles = ((int64_t)sorted_ids->numel_ / BM) * p.n_tiles;
+    launch_gemm<1>(tmap, p, max_tiles, a1->device_id, stream);
+}
+
+void launch_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* a2_scale, const aiter_tensor_t* w2,
+                       const aiter_tensor_t* w2_scale, const aiter_tensor_t* sorted_ids,
+                       const aiter_tensor_t* sorted_w, const aiter_tensor_t* sorted_eids,
+                       const aiter_tensor_t* num_valid, aiter_tensor_t* acc, aiter_tensor_t* status,
+                       cudaStream_t stream) {
+    check_tensor(a2, "a2", AITER_DTYPE_fp8, 2);
+    check_tensor(a2_scale, "a2_scale", AITER_DTYPE_fp32, -1);
+    check_tensor(w2, "w2", AITER_DTYPE_fp8, 3);
+    check_tensor(w2_scale, "w2_scale", AITER_DTYPE_fp32, -1);
+    check_tensor(sorted_ids, "sorted_token_ids", AITER_DTYPE_i32, 1);
+    check_tensor(sorted_w, "sorted_weights", AITER_DTYPE_fp32, 1);
+    check_tensor(sorted_eids, "sorted_expert_ids", AITER_DTYPE_i32, 1);
+    check_tensor(num_valid, "num_valid_ids", AITER_DTYPE_i32, 1);
+    check_tensor(acc, "acc", AITER_DTYPE_fp32, 2);
+    check_tensor(status, "status", AITER_DTYPE_i32, -1);
+    const int64_t P = a2->shape[0], I = a2->shape[1];
+    const int64_t E = w2->shape[0], H = w2->shape[1];
+    const int64_t M = acc->shape[0];
+    B200_CHECK(w2->shape[2] == I, "w2 must be [E, model_dim, inter_dim]: K ", w2->shape[2], " != ", I);
+    B200_CHECK(acc->shape[1] == H, "acc must be [M, model_dim]");
+    B200_CHECK(I % 128 == 0 && H % 128 == 0, "inter_dim and model_dim must be multiples of 128");
+    B200_CHECK((int64_t)a2_scale->numel_ >= P * (I / 128), "a2_scale must have P*inter_dim/128 elements");
+    B200_CHECK((int64_t)w2_scale->numel_ == E * (H / 128) * (I / 128),
+               "w2_scale must have E*(model_dim/128)*(inter_dim/128) elements");
+    B200_CHECK(P >= (int64_t)sorted_ids->numel_ && sorted_w->numel_ >= sorted_ids->numel_,
+               "a2 and sorted_weights must cover sorted_token_ids");
+    B200_CHECK(num_valid->numel_ >= 2 && status->numel_ >= 1, "num_valid_ids needs 2 and status 1 element");
+    B200_CHECK(E * H < ((int64_t)1 << 31) && M < (1 << 24), "problem too large");
+    B200_CHECK(((uintptr_t)a2->ptr & 15) == 0 && ((uintptr_t)w2->ptr & 15) == 0 && ((uintptr_t)acc->ptr & 15) == 0,
+               "a2, w2 and acc must be 16-byte aligned");
+
+    GemmParams p{};
+    p.a = (const uint8_t*)a2->ptr;
+    p.a_scale = (const float*)a2_scale->ptr;
+    p.w_scale = (const float*)w2_scale->ptr;
+    p.sorted_ids = (const int*)sorted_ids->ptr;
+    p.sorted_w = (const float*)sorted_w->ptr;
+    p.sorted_eids = (const int*)sorted_eids->ptr;
+    p.num_valid = (const int*)num_valid->ptr;
+    p.M = (int)M;
+    p.K = (int)I;
+    p.KB = (int)(I / 128);
+    p.n_tiles = (int)((H + 255) / 256);
+    p.n_rows = (int)H;
+    p.inter = (int)I;
+    p.acc = (float*)acc->ptr;
+    p.status = (int*)status->ptr;
+    CUtensorMap tmap = make_weight_map(w2->ptr, (uint64_t)(E * H), (uint64_t)I);
+    const int64_t max_tiles = ((int64_t)sorted_ids->numel_ / BM) * p.n_tiles;
+    launch_gemm<2>(tmap, p, max_tiles, a2->device_id, stream);
+}
+
+}  // namespace b200

@@ -1,0 +1,81 @@
+// Per-row, per-128-column dynamic FP8 e4m3 quantisation (bandwidth kernel).
+// Rounding sequence of the reference's torch oracle (aiter/ops/quant.py:64-94):
+//   amax -> scale = amax / 448 (IEEE division; 0 -> 1) -> code = RNE_e4m3(x / scale) (IEEE division)
+// so the codes and scales are bit-identical to it.  The reference's HIP kernel multiplies by
+// reciprocals instead (csrc/kernels/quant_kernels.cu:121,159-160), which is not.
+//
+// 16 lanes own one 128-element group (8 bf16 = one 16-byte load each), two groups per warp.
+
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kQuantThreads = 256;
+constexpr int kGroupsPerBlock = kQuantThreads / 16;
+
+__global__ void __launch_bounds__(kQuantThreads) quant_1x128_kernel(
+    const uint4* __restrict__ x, uint2* __restrict__ q, float* __restrict__ scales, int64_t groups) {
+    const int64_t g = (int64_t)blockIdx.x * kGroupsPerBlock + (threadIdx.x >> 4);
+    const int sub = threadIdx.x & 15;
+    const bool live = g < groups;
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (live) raw = __ldg(x + g * 16 + sub);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float2 f = __bfloat1622float2(h[i]);
+        v[2 * i] = f.x;
+        v[2 * i + 1] = f.y;
+    }
+    float amax = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+    for (int d = 8; d >= 1; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+    float scale = __fdiv_rn(amax, 448.0f);
+    if (scale == 0.f) scale = 1.f;
+    uint32_t w[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        float2 lo = make_float2(__fdiv_rn(v[4 * i], scale), __fdiv_rn(v[4 * i + 1], scale));
+        float2 hi = make_float2(__fdiv_rn(v[4 * i + 2], scale), __fdiv_rn(v[4 * i + 3], scale));
+        uint32_t a = __nv_cvt_float2_to_fp8x2(lo, __NV_SATFINITE, __NV_E4M3);
+        uint32_t b = __nv_cvt_float2_to_fp8x2(hi, __NV_SATFINITE, __NV_E4M3);
+        w[i] = a | (b << 16);
+    }
+    if (live) {
+        q[g * 16 + sub] = make_uint2(w[0], w[1]);
+        if (sub == 0) scales[g] = scale;
+    }
+}
+
+}  // namespace
+
+void launch_quant_1x128(aiter_tensor_t* out, const aiter_tensor_t* input, aiter_tensor_t* scales,
+                        cudaStream_t stream) {
+    check_tensor(input, "input", AITER_DTYPE_bf16, -1);
+    check_tensor(out, "out", AITER_DTYPE_fp8, -1);
+    check_tensor(scales, "scales", AITER_DTYPE_fp32, -1);
+    B200_CHECK(input->ndim >= 1, "input must have at least one dimension");
+    const int64_t cols = input->shape[input->ndim - 1];
+    B200_CHECK(cols % 128 == 0, "last dimension must be a multiple of 128, got ", cols);
+    B200_CHECK(out->numel_ == input->numel_, "out must have as many elements as input");
+    const int64_t groups = (int64_t)input->numel_ / 128;
+    B200_CHECK((int64_t)scales->numel_ >= groups, "scales needs ", groups, " elements, has ",
+               scales->numel_);
+    B200_CHECK(((uintptr_t)input->ptr & 15) == 0 && ((uintptr_t)out->ptr & 7) == 0,
+               "input must be 16-byte and out 8-byte aligned");
+    if (groups == 0) return;
+    const int64_t blocks = (groups + kGroupsPerBlock - 1) / kGroupsPerBlock;
+    B200_CHECK(blocks < ((int64_t)1 << 31), "input too large");
+    quant_1x128_kernel<<<(unsigned)blocks, kQuantThreads, 0, stream>>>(
+        (const uint4*)input->ptr, (uint2*)out->ptr, (float*)scales->ptr, groups);
+    B200_CUDA(cudaGetLastError());
+}
+
+}  // namespace b200

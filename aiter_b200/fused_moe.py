@@ -1,0 +1,290 @@
+"""Host side of the FP8 block-scaled fused-MoE path, behind the reference's own signatures.
+
+``fused_moe`` and ``moe_sorting`` keep the names, argument order and defaults of
+aiter/fused_moe.py:458-494 and :341-355, so a caller written for the reference runs unchanged.
+Everything that computes is a hand-written sm_100a kernel reached through the C-ABI of
+libaiter_b200.so (``_lib.call``); torch is used for device memory and streams only.  There is no
+tuned-config dispatch and no fallback: options outside the FP8 1x128 / 128x128 path raise
+``NotImplementedError`` naming the argument.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from . import dtypes
+from .enums import ActivationType, QuantType
+
+BLOCK_SIZE_M = 32          # default padding unit of moe_sorting (aiter/fused_moe.py:63)
+GEMM_BLOCK_M = 128         # row tile of the tcgen05 GEMM kernels == sort unit used by fused_moe
+
+# aiter/fused_moe.py:1310
+quant_remap = {QuantType.per_128x128: QuantType.per_1x128}
+
+_status_words: dict[int, torch.Tensor] = {}
+
+
+def _status(device: torch.device) -> torch.Tensor:
+    """Per-device int32 word the GEMM kernels set if a bounded device-side wait runs out."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _status_words:
+        _status_words[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status_words[idx]
+
+
+def check_device_status(device=None) -> None:
+    """Synchronises and raises if a kernel reported a timed-out wait since the last check."""
+    for idx, word in list(_status_words.items()):
+        if device is not None and torch.device(device).index not in (None, idx):
+            continue
+        if int(word.item()) != 0:
+            word.zero_()
+            raise RuntimeError("aiter_b200: a GEMM kernel gave up on a device-side wait "
+                               f"(cuda:{idx}); its output is incomplete")
+
+
+# ------------------------------------------------------------------------------------- sorting
+def moe_sorting_get_workspace_size(tokens: int, num_experts: int, topk: int) -> int:
+    """aiter/ops/moe_sorting_opus.py:12-18."""
+    return int(_lib.lib().b200_moe_sorting_get_workspace_size(int(tokens), int(num_experts), int(topk)))
+
+
+def moe_sorting(
+    topk_ids,
+    topk_weights,
+    num_experts,
+    model_dim,
+    moebuf_dtype,
+    block_size=BLOCK_SIZE_M,
+    expert_mask=None,
+    num_local_tokens=None,
+    dispatch_policy=0,
+    return_local_topk_ids=False,
+    accumulate=True,
+    flat=False,
+    output_aux=False,
+):
+    """aiter/fused_moe.py:341-406 / _moe_sorting_impl :175-288.
+
+    Returns (sorted_ids, sorted_weights, sorted_expert_ids, num_valid_ids, moe_buf)
+    (+ local_topk_ids when asked).  moe_buf is [M, model_dim] and zero-filled when
+    ``accumulate`` or ``expert_mask`` is given, else a (0, 0) placeholder."""
+    if flat:
+        raise NotImplementedError("moe_sorting: flat=True (unsorted pass-through) is not supported")
+    if output_aux:
+        raise NotImplementedError("moe_sorting: output_aux=True is not supported")
+    if not topk_ids.is_cuda:
+        raise RuntimeError("moe_sorting: topk_ids must be a CUDA tensor (there is no CPU path)")
+    device = topk_ids.device
+    M, topk = topk_ids.shape
+    block_size = int(block_size)
+    max_num_tokens_padded = int(topk_ids.numel() + num_experts * block_size - topk)
+    max_num_m_blocks = int((max_num_tokens_padded + block_size - 1) // block_size)
+    sorted_ids = torch.empty(max_num_tokens_padded, dtype=dtypes.i32, device=device)
+    sorted_weights = torch.empty(max_num_tokens_padded, dtype=dtypes.fp32, device=device)
+    sorted_expert_ids = torch.empty(max_num_m_blocks, dtype=dtypes.i32, device=device)
+    num_valid_ids = torch.empty(2, dtype=dtypes.i32, device=device)
+    if (expert_mask is not None) or accumulate:
+        moe_buf = torch.empty((M, model_dim), dtype=moebuf_dtype, device=device)
+    else:
+        moe_buf = torch.empty((0, 0), dtype=moebuf_dtype, device=device)
+    local_topk_ids = torch.empty_like(topk_ids) if return_local_topk_ids else None
+    ws_size = moe_sorting_get_workspace_size(M, num_experts, topk)
+    workspace = torch.empty(ws_size, dtype=torch.uint8, device=device) if ws_size > 0 else None
+    _lib.call(
+        "b200_moe_sorting_fwd",
+        topk_ids.contiguous(), topk_weights.contiguous(), sorted_ids, sorted_weights, sorted_expert_ids,
+        num_valid_ids, moe_buf if moe_buf.numel() > 0 else None, int(num_experts), block_size,
+        expert_mask, num_local_tokens, workspace, int(dispatch_policy), local_topk_ids,
+        device=device,
+    )
+    ret = (sorted_ids, sorted_weights, sorted_expert_ids, num_valid_ids, moe_buf)
+    if return_local_topk_ids:
+        return (*ret, local_topk_ids)
+    return ret
+
+
+# ------------------------------------------------------------------------------------- quant
+def per_group_quant_hip(x, scale=None, quant_dtype=dtypes.fp8, group_size=128, transpose_scale=False,
+                        num_rows=None, num_rows_factor=1):
+    """1x128 dynamic FP8 quantisation, signature of aiter/ops/quant.py:439-483.
+    x [..., C] bf16 -> (codes [..., C] e4m3, scales [rows, C/128] fp32)."""
+    if group_size != 128:
+        raise NotImplementedError("per_group_quant_hip: only group_size=128 is supported")
+    if quant_dtype != dtypes.fp8:
+        raise NotImplementedError("per_group_quant_hip: only quant_dtype=fp8 (e4m3fn) is supported")
+    if transpose_scale:
+        raise NotImplementedError("per_group_quant_hip: transpose_scale=True is not supported")
+    if scale is not None or num_rows is not None:
+        raise NotImplementedError("per_group_quant_hip: static scale / num_rows are not supported")
+    if x.dtype != dtypes.bf16:
+        raise NotImplementedError(f"per_group_quant_hip: input must be bf16, got {x.dtype}")
+    x = x.contiguous()
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    y = torch.empty(x.shape, dtype=dtypes.fp8, device=x.device)
+    y_scale = torch.empty((rows, cols // 128), dtype=dtypes.fp32, device=x.device)
+    _lib.call("b200_moe_quant_1x128", y, x, y_scale, device=x.device)
+    return y, y_scale
+
+
+def get_hip_quant(qType):
+    """aiter/ops/quant.py:367-387, restricted to the block-scale path."""
+    qType = quant_remap.get(QuantType(qType), QuantType(qType))
+    if qType != QuantType.per_1x128:
+        raise NotImplementedError(f"get_hip_quant: only per_1x128 / per_128x128 are supported, got {qType!r}")
+    return per_group_quant_hip
+
+
+# ------------------------------------------------------------------------------------- fused_moe
+def _check_unsupported(**kw):
+    for name, (value, neutral) in kw.items():
+        bad = (value is not None) if neutral is None else (value != neutral)
+        if bad:
+            raise NotImplementedError(f"fused_moe: {name}={value!r} is not supported by the B200 "
+                                      "FP8 block-scale path")
+
+
+def get_inter_dim(w1_shape, w2_shape):
+    """aiter/fused_moe.py:448-456."""
+    E, _, model_dim = w1_shape
+    E, model_dim, inter_dim = w2_shape
+    return E, model_dim, inter_dim
+
+
+def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, w1_scale, w2_scale,
+                     a1_scale, num_local_tokens, dtype, return_intermediates=False):
+    """sort -> a1 quant -> stage 1 -> stage 2 -> final rounding (the 2-stage flow of
+    aiter/fused_moe.py:2979-3368 with the requant fused into stage 1)."""
+    device = hidden_states.device
+    M, topk = topk_ids.shape
+    E, model_dim, inter_dim = get_inter_dim(w1.shape, w2.shape)
+    global_E = expert_mask.numel() if expert_mask is not None else E
+
+    sorted_ids, sorted_weights, sorted_expert_ids, num_valid_ids, _ = moe_sorting(
+        topk_ids, topk_weight, global_E, model_dim, dtype, GEMM_BLOCK_M, expert_mask,
+        num_local_tokens, 0, accumulate=False)
+    if expert_mask is not None:
+        pass  # moe_buf returned for API parity only; stage 2 accumulates in its own fp32 buffer
+
+    if hidden_states.dtype == dtypes.fp8:
+        a1, a1_s = hidden_states.contiguous(), a1_scale.contiguous().view(M, -1)
+    else:
+        a1, a1_s = per_group_quant_hip(hidden_states)
+
+    P = sorted_ids.numel()
+    a2 = torch.empty((P, inter_dim), dtype=dtypes.fp8, device=device)
+    a2_s = torch.empty((P, inter_dim // 128), dtype=dtypes.fp32, device=device)
+    status = _status(device)
+    _lib.call("b200_moe_stage1", a1, a1_s, w1, w1_scale, sorted_ids, sorted_expert_ids, num_valid_ids,
+              a2, a2_s, status, device=device)
+    acc = torch.zeros((M, model_dim), dtype=dtypes.fp32, device=device)
+    _lib.call("b200_moe_stage2", a2, a2_s, w2, w2_scale, sorted_ids, sorted_weights, sorted_expert_ids,
+              num_valid_ids, acc, status, device=device)
+    out = torch.empty((M, model_dim), dtype=dtype, device=device)
+    _lib.call("b200_moe_finalize", out, acc, device=device)
+    if return_intermediates:
+        return out, dict(sorted_ids=sorted_ids, sorted_weights=sorted_weights,
+                         sorted_expert_ids=sorted_expert_ids, num_valid_ids=num_valid_ids,
+                         a1=a1, a1_scale=a1_s, a2=a2, a2_scale=a2_s, acc=acc)
+    return out
+
+
+def fused_moe(
+    hidden_states,
+    w1,  # [expert(local_expert:EP), inter_dim*2, dim] N,K
+    w2,  # [expert(local_expert:EP), dim, inter_dim]
+    topk_weight,
+    topk_ids,
+    expert_mask=None,  # EP
+    activation=ActivationType.Silu,
+    quant_type=QuantType.No,
+    doweight_stage1=False,
+    # following for quant
+    w1_scale=None,  # [expert, 2*inter_dim/128, dim/128] (or any shape with that many elements)
+    w2_scale=None,  # [expert, dim/128, inter_dim/128]
+    a1_scale=None,  # [tokens, dim/128] when hidden_states is already fp8
+    a2_scale=None,
+    # following for tuning
+    block_size_M=None,
+    num_local_tokens=None,
+    moe_sorting_dispatch_policy=0,
+    dtype=None,
+    # following for cktile support
+    hidden_pad=0,
+    intermediate_pad=0,
+    bias1=None,
+    bias2=None,
+    splitk=0,
+    swiglu_limit=None,
+    beta=None,
+    linear_beta=None,
+    gate_mode="separated",
+    shared_w1=None,
+    shared_w2=None,
+    shared_w1_scale=None,
+    shared_w2_scale=None,
+    shared_expert_id=-1,
+    stage2_scatter=None,
+):
+    """Drop-in for aiter.fused_moe (aiter/fused_moe.py:458-576) on the FP8 block-scale path.
+
+    hidden_states [M, H] bf16 (or e4m3 + a1_scale [M, H/128]); w1 [E, 2I, H] e4m3, gate rows then
+    up rows; w2 [E, H, I] e4m3; w1_scale/w2_scale fp32 per 128x128 block; topk_weight [M, topk]
+    fp32; topk_ids [M, topk] int32 (global expert ids when expert_mask is given).  Returns [M, H]
+    in ``dtype`` (default: hidden_states.dtype; bf16 when that is fp8).
+
+    ``block_size_M`` is accepted and ignored: the GEMM row tile is fixed at 128, which only
+    changes how the routes are padded, not the result."""
+    quant_type = quant_remap.get(QuantType(quant_type), QuantType(quant_type))
+    if quant_type != QuantType.per_1x128:
+        raise NotImplementedError(
+            f"fused_moe: quant_type={QuantType(quant_type)!r} is not supported; this build covers "
+            "QuantType.per_1x128 / per_128x128 (FP8 block scale)")
+    if ActivationType(activation) != ActivationType.Silu:
+        raise NotImplementedError(f"fused_moe: activation={ActivationType(activation)!r} is not supported (Silu only)")
+    _check_unsupported(
+        doweight_stage1=(bool(doweight_stage1), False), a2_scale=(a2_scale, None),
+        hidden_pad=(hidden_pad, 0), intermediate_pad=(intermediate_pad, 0), bias1=(bias1, None),
+        bias2=(bias2, None), splitk=(splitk or 0, 0), swiglu_limit=(swiglu_limit, None),
+        beta=(beta, None), linear_beta=(linear_beta, None), shared_w1=(shared_w1, None),
+        shared_w2=(shared_w2, None), shared_w1_scale=(shared_w1_scale, None),
+        shared_w2_scale=(shared_w2_scale, None), shared_expert_id=(shared_expert_id, -1),
+        stage2_scatter=(stage2_scatter, None))
+    if gate_mode not in (None, "separated"):
+        raise NotImplementedError(f"fused_moe: gate_mode={gate_mode!r} is not supported (separated only)")
+    if not hidden_states.is_cuda:
+        raise RuntimeError("fused_moe: tensors must live on a CUDA device (there is no CPU path)")
+    if w1.dtype != dtypes.fp8 or w2.dtype != dtypes.fp8:
+        raise NotImplementedError(f"fused_moe: weights must be float8_e4m3fn, got {w1.dtype}/{w2.dtype}")
+    if w1_scale is None or w2_scale is None:
+        raise ValueError("fused_moe: w1_scale and w2_scale are required for block-scale quantisation")
+    M, topk = topk_ids.shape
+    E, model_dim, inter_dim = get_inter_dim(w1.shape, w2.shape)
+    if w1.shape[1] != 2 * inter_dim:
+        raise NotImplementedError(f"fused_moe: only gated (g1u1) weights are supported: {w1.shape=} {w2.shape=}")
+    if inter_dim % 128 != 0 or model_dim % 128 != 0:
+        # csrc/py_itfs_cu/asm_fmoe.cu:926, gemm_moe_ck2stages_common_blockscale.cuh:106-108
+        raise ValueError(f"fused_moe: inter_dim ({inter_dim}) and model_dim ({model_dim}) must be multiples of 128")
+    if hidden_states.shape != (M, model_dim):
+        raise ValueError(f"fused_moe: hidden_states must be [{M}, {model_dim}], got {tuple(hidden_states.shape)}")
+    if hidden_states.dtype == dtypes.fp8:
+        if a1_scale is None:
+            raise ValueError("fused_moe: fp8 hidden_states need a1_scale [M, model_dim/128]")
+        dtype = dtypes.bf16 if dtype is None else dtype
+    else:
+        if hidden_states.dtype != dtypes.bf16:
+            raise NotImplementedError(f"fused_moe: hidden_states must be bf16 or pre-quantised fp8, got {hidden_states.dtype}")
+        if a1_scale is not None:
+            raise NotImplementedError("fused_moe: a1_scale with un-quantised hidden_states is not supported")
+        dtype = hidden_states.dtype if dtype is None else dtype
+    # aiter/fused_moe.py:752-756
+    assert dtype in [dtypes.fp16, dtypes.bf16], f"Fused_moe unsupported out dtype: {dtype}"
+    if topk_weight.dtype != dtypes.fp32:
+        raise ValueError("fused_moe: topk_weight must be float32")
+    if topk_ids.dtype != dtypes.i32:
+        raise ValueError("fused_moe: topk_ids must be int32")
+    return fused_moe_stages(hidden_states, w1.contiguous(), w2.contiguous(), topk_weight, topk_ids,
+                            expert_mask, w1_scale.contiguous(), w2_scale.contiguous(), a1_scale,
+                            num_local_tokens, dtype)

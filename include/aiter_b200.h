@@ -1,0 +1,127 @@
+/*
+ * C-ABI of libaiter_b200.so: the FP8 block-scaled fused-MoE path for NVIDIA B200 (sm_100a).
+ *
+ * Calling convention (the one ROCm/aiter's ctypes FFI binds, aiter/jit/core.py:1306-1620):
+ *   - every entry point returns int: 0 = success, -1 = failure; the message of the last
+ *     failure on the calling thread is read with aiter_get_last_error()
+ *     (csrc/include/aiter_ctypes_error.h:55-155);
+ *   - tensors travel as pointers to the 160-byte POD aiter_tensor_t
+ *     (csrc/include/aiter_tensor.h:8-18); an absent optional tensor is NULL;
+ *   - the caller owns every buffer (inputs, outputs and workspaces); the library never
+ *     allocates, frees or retains device memory, and never synchronises the host;
+ *   - the CUDA stream is the last argument (NULL = the legacy default stream); work is
+ *     enqueued on the device that holds the first tensor argument.
+ *
+ * All tensors must be contiguous.  Paths are relative to the ROCm/aiter tree.
+ */
+#ifndef AITER_B200_H
+#define AITER_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* csrc/include/aiter_enum.h:36-52 */
+typedef enum {
+    AITER_DTYPE_fp8 = 0,
+    AITER_DTYPE_fp8_e8m0,
+    AITER_DTYPE_fp16,
+    AITER_DTYPE_bf16,
+    AITER_DTYPE_fp32,
+    AITER_DTYPE_i4x2,
+    AITER_DTYPE_fp4x2,
+    AITER_DTYPE_u32,
+    AITER_DTYPE_i32,
+    AITER_DTYPE_i16,
+    AITER_DTYPE_i8,
+    AITER_DTYPE_u8,
+    AITER_DTYPE_i64,
+    AITER_DTYPE_u64
+} AiterDtype;
+
+/* csrc/include/aiter_tensor.h:8-18 */
+typedef struct aiter_tensor_t {
+    void*   ptr;        /* device pointer                     */
+    size_t  numel_;     /* number of elements                 */
+    int     ndim;       /* number of dimensions (<= 8)        */
+    int64_t shape[8];
+    int64_t strides[8]; /* in elements                        */
+    int     dtype_;     /* AiterDtype                         */
+    int     device_id;  /* CUDA device index, -1 = host       */
+} aiter_tensor_t;
+
+/* csrc/include/aiter_ctypes_error.h:61-71 */
+int         aiter_ctypes_abi_version(void); /* == 2 */
+const char* aiter_get_last_error(void);     /* NULL when no error is pending */
+void        aiter_clear_last_error(void);
+
+/* Bytes of scratch b200_moe_sorting_fwd needs for this problem (0 when the single-CTA
+ * path is taken).  Replaces moe_sorting_opus_get_workspace_size
+ * (aiter/ops/moe_sorting_opus.py:12-18, csrc/include/moe_sorting_opus.h:1385-1427). */
+int64_t b200_moe_sorting_get_workspace_size(int tokens, int num_experts, int topk);
+
+/* Stable counting sort of (token, slot) routes by expert, padded per expert to unit_size.
+ * Replaces moe_sorting_opus_fwd (csrc/py_itfs_cu/moe_sorting_opus_kernels.cu:14-84,
+ * argument order of aiter/ops/moe_sorting_opus.py:21-38).
+ *   topk_ids [M,topk] i32, topk_weights [M,topk] fp32
+ *   sorted_token_ids [P] i32 = slot<<24|token, pads = topk<<24|M   (P = M*topk + E*unit - topk)
+ *   sorted_weights [P] fp32 (0 in pads), sorted_expert_ids [ceil(P/unit)] i32 (local ids, -1 past the end)
+ *   num_valid_ids [2] i32 = {padded total, tokens sorted}
+ *   moe_buf: optional [M, model_dim] buffer that is zero-filled (any dtype)
+ *   local_expert_mask: optional [E] i32, 0 drops the expert and renumbers the others
+ *   num_local_tokens: optional [1] i32 read on the device (rows >= it are ignored)
+ *   workspace: >= b200_moe_sorting_get_workspace_size bytes when that is > 0
+ *   local_topk_ids: optional [M,topk] i32 output, local expert id per route or -1 */
+int b200_moe_sorting_fwd(const aiter_tensor_t* topk_ids, const aiter_tensor_t* topk_weights,
+                         aiter_tensor_t* sorted_token_ids, aiter_tensor_t* sorted_weights,
+                         aiter_tensor_t* sorted_expert_ids, aiter_tensor_t* num_valid_ids,
+                         aiter_tensor_t* moe_buf, int num_experts, int unit_size,
+                         const aiter_tensor_t* local_expert_mask,
+                         const aiter_tensor_t* num_local_tokens, aiter_tensor_t* workspace,
+                         int dispatch_policy, aiter_tensor_t* local_topk_ids, void* stream);
+
+/* Dynamic per-row, per-128-column FP8 e4m3 quantisation: scale = amax/448 (1 when amax is 0),
+ * codes = RNE(x / scale).  Replaces dynamic_per_token_scaled_quant with group_size=128
+ * (aiter/ops/quant.py:439-483, csrc/kernels/quant_kernels.cu:27-167,720-830) with the
+ * rounding sequence of the torch oracle (aiter/ops/quant.py:64-94).
+ *   input [R,C] bf16 (C % 128 == 0) -> out [R,C] fp8, scales [R,C/128] fp32 */
+int b200_moe_quant_1x128(aiter_tensor_t* out, const aiter_tensor_t* input, aiter_tensor_t* scales,
+                         void* stream);
+
+/* Stage 1: grouped gate/up GEMM over the sorted blocks + SiLU(gate)*up + bf16 rounding +
+ * 1x128 FP8 requantisation.  Replaces ck_moe_stage1 followed by the a2 quant
+ * (csrc/ck_gemm_moe_2stages_codegen/gemm_moe_ck2stages.cu:68-137, aiter/fused_moe.py:3220-3336).
+ * The sort must have used unit_size == 128.
+ *   a1 [M,H] fp8 + a1_scale [M,H/128] fp32; w1 [E,2I,H] fp8 (gate rows then up rows) +
+ *   w1_scale [E,2I/128,H/128] fp32
+ *   a2 [P,I] fp8 and a2_scale [P,I/128] fp32, rows in SORTED order (row p belongs to
+ *   sorted_token_ids[p]; rows of pads are zero)
+ *   status [1] i32 device word: set non-zero if a bounded device-side wait ran out */
+int b200_moe_stage1(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale,
+                    const aiter_tensor_t* w1, const aiter_tensor_t* w1_scale,
+                    const aiter_tensor_t* sorted_token_ids, const aiter_tensor_t* sorted_expert_ids,
+                    const aiter_tensor_t* num_valid_ids, aiter_tensor_t* a2, aiter_tensor_t* a2_scale,
+                    aiter_tensor_t* status, void* stream);
+
+/* Stage 2: grouped down GEMM over the sorted blocks, times the route weight, accumulated
+ * per token in fp32.  Replaces ck_moe_stage2
+ * (csrc/ck_gemm_moe_2stages_codegen/gemm_moe_ck2stages.cu:139-199).
+ *   a2/a2_scale as written by stage 1; w2 [E,H,I] fp8 + w2_scale [E,H/128,I/128] fp32
+ *   acc [M,H] fp32, must be zero on entry; receives sum over routes of weight * (a2 . w2) */
+int b200_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* a2_scale,
+                    const aiter_tensor_t* w2, const aiter_tensor_t* w2_scale,
+                    const aiter_tensor_t* sorted_token_ids, const aiter_tensor_t* sorted_weights,
+                    const aiter_tensor_t* sorted_expert_ids, const aiter_tensor_t* num_valid_ids,
+                    aiter_tensor_t* acc, aiter_tensor_t* status, void* stream);
+
+/* out[M,H] (bf16 or fp16) = round-to-nearest-even(acc[M,H] fp32): the single final rounding of
+ * the reference's `out.sum(1).to(dtype)` (aiter/fused_moe.py:3811). */
+int b200_moe_finalize(aiter_tensor_t* out, const aiter_tensor_t* acc, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AITER_B200_H */
