@@ -42,7 +42,7 @@ _SIGNATURES = {
                                                 ctypes.c_int, _T, ctypes.c_void_p]),
     "b200_moe_quant_1x128": (ctypes.c_int, [_T] * 3 + [ctypes.c_void_p]),
     "b200_moe_stage1": (ctypes.c_int, [_T] * 10 + [ctypes.c_void_p]),
-    "b200_moe_stage2": (ctypes.c_int, [_T] * 11 + [ctypes.c_void_p]),
+    "b200_moe_stage2": (ctypes.c_int, [_T] * 10 + [ctypes.c_void_p]),
     "b200_moe_finalize": (ctypes.c_int, [_T] * 2 + [ctypes.c_void_p]),
 }
 

@@ -332,16 +332,17 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
     }
 
     // ------------------------------------------------------------------------ tail
-    if (*abort_flag) {
-        if (threadIdx.x == 0) atomicExch(p.status, 1);
-        // give copies / MMAs still in flight a bounded time to land before TMEM is released
-        const long long t0 = clock64();
-        while (clock64() - t0 < 2000000LL) {
-        }
-    }
     ptx::tc_fence_before();
     __syncthreads();
+    const bool gave_up = *abort_flag != 0;
+    if (gave_up && threadIdx.x == 0) atomicExch(p.status, 1);
     if (warp == 2) {
+        if (gave_up) {
+            // give copies / MMAs still in flight a bounded time to land before TMEM is released
+            const long long t0 = clock64();
+            while (clock64() - t0 < 2000000LL) {
+            }
+        }
         ptx::tc_fence_after();
         ptx::tmem_dealloc(tmem_base, kTmemCols);
     }

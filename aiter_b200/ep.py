@@ -1,0 +1,88 @@
+"""Expert parallelism for the fused-MoE layer: one process per GPU, NCCL over NVLink/NVSwitch.
+
+Rank r owns experts [r*E/G, (r+1)*E/G) and token rows [r*M/G, (r+1)*M/G).  One exchange on each
+side of the local layer:
+
+  1. 1x128-quantise the local rows, all-gather the e4m3 codes, their fp32 scales and the routing
+     (ids + weights), so every rank holds all M rows in 1 byte per element;
+  2. fused_moe stages on all rows with ``expert_mask`` = this rank's experts and global ids: the
+     sort drops non-local routes, stage 2 leaves an fp32 partial sum [M, H];
+  3. reduce-scatter(sum) of the fp32 partials, then the single final rounding to bf16 on the
+     rank's own rows.
+
+Reducing in fp32 keeps the result equal to the single-GPU one up to fp32 summation order.  The
+reference reaches the same end with an all-to-all dispatch/combine
+(op_tests/multigpu_tests/test_dispatch_combine.py:75-177, oracle run_ref :18-72).
+
+The collectives go through ``torch.distributed`` so the same code runs on gloo/CPU ranks for the
+host-logic tests; ``local_layer`` is injectable for that purpose.
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+from . import _lib, dtypes
+from .fused_moe import fused_moe_stages, per_group_quant_hip
+
+
+def expert_mask_for_rank(num_experts: int, rank: int, world: int, device=None) -> torch.Tensor:
+    """[global_E] int32, 1 for the contiguous slice of experts owned by ``rank``."""
+    if num_experts % world != 0:
+        raise ValueError(f"num_experts ({num_experts}) must be divisible by the EP world size ({world})")
+    per = num_experts // world
+    mask = torch.zeros(num_experts, dtype=torch.int32, device=device)
+    mask[rank * per:(rank + 1) * per] = 1
+    return mask
+
+
+def _gpu_local_layer(a1, a1_scale, w1, w2, topk_weight, topk_ids, expert_mask, w1_scale, w2_scale):
+    """All rows, local experts -> fp32 partial [M, H] (no final rounding)."""
+    _, inter = fused_moe_stages(a1, w1, w2, topk_weight, topk_ids, expert_mask, w1_scale, w2_scale,
+                                   a1_scale, None, dtypes.bf16, return_intermediates=True)
+    return inter["acc"]
+
+
+def _gpu_quant(x):
+    return per_group_quant_hip(x)
+
+
+def _gpu_finalize(acc, dtype):
+    out = torch.empty(acc.shape, dtype=dtype, device=acc.device)
+    _lib.call("b200_moe_finalize", out, acc, device=acc.device)
+    return out
+
+
+def ep_fused_moe(x_local, w1_local, w2_local, topk_weight_local, topk_ids_local, w1_scale_local,
+                 w2_scale_local, num_experts, group=None, dtype=torch.bfloat16,
+                 quant=_gpu_quant, local_layer=_gpu_local_layer, finalize=_gpu_finalize):
+    """x_local [M/G, H] bf16, routing [M/G, topk] with GLOBAL expert ids -> out [M/G, H].
+
+    Every rank must pass the same number of rows."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    m_local, H = x_local.shape
+    topk = topk_ids_local.shape[1]
+    dev = x_local.device
+    a1_l, a1s_l = quant(x_local)
+    if world == 1:
+        a1, a1s, ids, wts = a1_l, a1s_l, topk_ids_local, topk_weight_local
+    else:
+        a1 = torch.empty((world * m_local, H), dtype=torch.uint8, device=dev)
+        a1s = torch.empty((world * m_local, H // 128), dtype=torch.float32, device=dev)
+        ids = torch.empty((world * m_local, topk), dtype=torch.int32, device=dev)
+        wts = torch.empty((world * m_local, topk), dtype=torch.float32, device=dev)
+        dist.all_gather_into_tensor(a1, a1_l.view(torch.uint8), group=group)
+        dist.all_gather_into_tensor(a1s, a1s_l.contiguous(), group=group)
+        dist.all_gather_into_tensor(ids, topk_ids_local.contiguous(), group=group)
+        dist.all_gather_into_tensor(wts, topk_weight_local.contiguous(), group=group)
+        a1 = a1.view(torch.float8_e4m3fn)
+    mask = expert_mask_for_rank(num_experts, rank, world, device=dev)
+    partial = local_layer(a1, a1s, w1_local, w2_local, wts, ids, mask, w1_scale_local, w2_scale_local)
+    if world == 1:
+        mine = partial
+    else:
+        mine = torch.empty((m_local, H), dtype=torch.float32, device=dev)
+        dist.reduce_scatter_tensor(mine, partial, op=dist.ReduceOp.SUM, group=group)
+    return finalize(mine, dtype)

@@ -153,21 +153,31 @@ def get_inter_dim(w1_shape, w2_shape):
     return E, model_dim, inter_dim
 
 
+def _mark(timers, name):
+    if timers is not None:
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        timers.append((name, ev))
+
+
 def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, w1_scale, w2_scale,
-                     a1_scale, num_local_tokens, dtype, return_intermediates=False):
+                     a1_scale, num_local_tokens, dtype, return_intermediates=False, timers=None):
     """sort -> a1 quant -> stage 1 -> stage 2 -> final rounding (the 2-stage flow of
-    aiter/fused_moe.py:2979-3368 with the requant fused into stage 1)."""
+    aiter/fused_moe.py:2979-3368 with the requant fused into stage 1).
+
+    ``timers``: optional list that receives (name, cuda event) marks recorded on the current
+    stream before each kernel and at the end (the reference's per-stage bench hook,
+    aiter/fused_moe.py:79-82)."""
     device = hidden_states.device
     M, topk = topk_ids.shape
     E, model_dim, inter_dim = get_inter_dim(w1.shape, w2.shape)
     global_E = expert_mask.numel() if expert_mask is not None else E
 
+    _mark(timers, "sort")
     sorted_ids, sorted_weights, sorted_expert_ids, num_valid_ids, _ = moe_sorting(
         topk_ids, topk_weight, global_E, model_dim, dtype, GEMM_BLOCK_M, expert_mask,
         num_local_tokens, 0, accumulate=False)
-    if expert_mask is not None:
-        pass  # moe_buf returned for API parity only; stage 2 accumulates in its own fp32 buffer
-
+    _mark(timers, "quant")
     if hidden_states.dtype == dtypes.fp8:
         a1, a1_s = hidden_states.contiguous(), a1_scale.contiguous().view(M, -1)
     else:
@@ -177,13 +187,18 @@ def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, 
     a2 = torch.empty((P, inter_dim), dtype=dtypes.fp8, device=device)
     a2_s = torch.empty((P, inter_dim // 128), dtype=dtypes.fp32, device=device)
     status = _status(device)
+    _mark(timers, "stage1")
     _lib.call("b200_moe_stage1", a1, a1_s, w1, w1_scale, sorted_ids, sorted_expert_ids, num_valid_ids,
               a2, a2_s, status, device=device)
+    _mark(timers, "zero")
     acc = torch.zeros((M, model_dim), dtype=dtypes.fp32, device=device)
+    _mark(timers, "stage2")
     _lib.call("b200_moe_stage2", a2, a2_s, w2, w2_scale, sorted_ids, sorted_weights, sorted_expert_ids,
               num_valid_ids, acc, status, device=device)
+    _mark(timers, "finalize")
     out = torch.empty((M, model_dim), dtype=dtype, device=device)
     _lib.call("b200_moe_finalize", out, acc, device=device)
+    _mark(timers, "end")
     if return_intermediates:
         return out, dict(sorted_ids=sorted_ids, sorted_weights=sorted_weights,
                          sorted_expert_ids=sorted_expert_ids, num_valid_ids=num_valid_ids,

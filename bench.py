@@ -1,0 +1,347 @@
+#!/usr/bin/env python
+"""Benchmark of the FP8 block-scaled fused-MoE layer (DeepSeek-V3 shape) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+One "step" is one pass of the layer over one batch of synthetic tokens (seeded N(0,1) activations,
+N(0,1/sqrt(K)) weights quantised to e4m3 per 128x128 block, DeepSeek-V3 grouped top-8 routing).
+Headline workload: M=8192 tokens, H=7168, I=2048, E=256, topk=8 (prefill); the M=64 decode case is
+measured in the same run and reported under "decode".  With N GPUs the experts are sharded
+(expert parallelism: token all-gather, local layer, fp32 reduce-scatter) and the total work stays
+fixed, so scaling is "strong".  Rank 0 prints ONE JSON line.
+
+`--impl reference` times the CPU oracle (the reference's torch arithmetic restated per expert) on
+the host cores over a bounded sample of the same workload.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+H, I, E, TOPK = 7168, 2048, 256, 8
+M_PREFILL, M_DECODE = 8192, 64
+WORKLOAD = "dsv3_fp8_blockscale_moe_prefill_M8192_H7168_I2048_E256_topk8"
+METRIC = "DSV3 FP8-blockscale fused_moe TFLOP/s (M=8192)"
+
+
+def flops(M):
+    return 6.0 * M * TOPK * H * I
+
+
+def algorithmic_bytes(M, n_active):
+    per_expert = 3 * H * I + 3 * H * I // 16384 * 4
+    return n_active * per_expert + 4 * M * H + 8 * M * TOPK
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"], source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.rows = []
+        self.proc = None
+        self.gpu = gpu_index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
+        self.proc.terminate()
+        self.t.join(timeout=2)
+        sm = [float(r[0]) for r in self.rows if len(r) >= 6 and r[0].replace(".", "").isdigit()]
+        mx = [float(r[1]) for r in self.rows if len(r) >= 6 and r[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i] == "Active" for r in self.rows)]
+        return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=reasons, samples=len(sm))
+
+
+# ------------------------------------------------------------------------------------------ inputs
+def make_layer(device, rank, world, seed=0):
+    """This rank's expert slice (weights drawn on the device) and the full routing."""
+    from oracle import inputs
+    e_local = E // world
+    w1_q, w1_s = inputs.make_weights(e_local, 2 * I, H, seed + 1 + 1000 * rank, device)
+    w2_q, w2_s = inputs.make_weights(e_local, H, I, seed + 2 + 1000 * rank, device)
+    return w1_q, w1_s, w2_q, w2_s
+
+
+def make_tokens(M, seed=0):
+    from oracle import inputs
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn((M, H), generator=g, dtype=torch.float32).to(torch.bfloat16)
+    tw, ti = inputs.make_routing("dsv3", M, E, TOPK, seed)
+    return x, tw, ti
+
+
+# ------------------------------------------------------------------------------------------ CPU arm
+def cpu_sample_step(x, tw, ti, w1_q, w1_s, w2_q, w2_s, n_exp):
+    """Oracle on the routes of the first ``n_exp`` experts (all tokens, 1/(E/n_exp) of the layer)."""
+    from oracle import moe_oracle
+    mask = torch.zeros(E, dtype=torch.int32)
+    mask[:n_exp] = 1
+    t0 = time.perf_counter()
+    moe_oracle.fused_moe_ref(x, w1_q[:n_exp], w1_s[:n_exp], w2_q[:n_exp], w2_s[:n_exp], tw, ti, expert_mask=mask)
+    dt = time.perf_counter() - t0
+    routes = int((ti < n_exp).sum())
+    return dt, 6.0 * routes * H * I
+
+
+def cpu_baseline(n_exp=8, steps=1, warmup=0, seed=0):
+    from oracle import inputs
+    cores = len(os.sched_getaffinity(0))
+    torch.set_num_threads(cores)
+    x, tw, ti = make_tokens(M_PREFILL, seed)
+    w1_q, w1_s = inputs.make_weights(n_exp, 2 * I, H, seed + 1)
+    w2_q, w2_s = inputs.make_weights(n_exp, H, I, seed + 2)
+    times, fl = [], 0.0
+    for i in range(warmup + steps):
+        dt, fl = cpu_sample_step(x, tw, ti, w1_q, w1_s, w2_q, w2_s, n_exp)
+        if i >= warmup:
+            times.append(dt)
+    t = sum(times) / len(times)
+    return dict(value=fl / t / 1e12, unit="TFLOP/s", cores=cores, kind="port",
+                sample=f"routes of experts 0..{n_exp - 1} of {E} over all {M_PREFILL} tokens "
+                       f"({fl / flops(M_PREFILL):.4f} of the layer's FLOPs), {len(times)} run(s), {t:.2f} s each",
+                seconds_per_step=t)
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    n_exp = 4
+    cb = cpu_baseline(n_exp=n_exp, steps=max(1, args.steps), warmup=min(args.warmup, 1))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["seconds_per_step"] * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp32 (e4m3 codes dequantised)",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "sample": cb["sample"]},
+        "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------ GPU arm
+def timed(fn, steps, warmup, sync, profile=False):
+    for _ in range(warmup):
+        fn()
+    sync()
+    if profile:
+        torch.cuda.profiler.start()
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    ev[0].record()
+    for i in range(steps):
+        fn()
+        ev[i + 1].record()
+    sync()
+    if profile:
+        torch.cuda.profiler.stop()
+    return [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]
+
+
+def kernel_breakdown(fm, dev_args, reps=5):
+    """Average device time of each kernel of the layer, from CUDA events on the launch stream."""
+    acc = {}
+    for _ in range(reps):
+        timers = []
+        fm.fused_moe_stages(*dev_args, timers=timers)
+        torch.cuda.synchronize()
+        for (n0, e0), (_n1, e1) in zip(timers[:-1], timers[1:]):
+            acc.setdefault(n0, []).append(e0.elapsed_time(e1))
+    return {k: sum(v) / len(v) for k, v in acc.items()}
+
+
+def main():
+    global M_PREFILL, E, WORKLOAD
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tokens", type=int, default=M_PREFILL, help="override M (profiling a small case)")
+    ap.add_argument("--experts", type=int, default=E, help="override E (profiling a small case)")
+    ap.add_argument("--skip-decode", action="store_true")
+    ap.add_argument("--cuda-profiler-range", action="store_true",
+                    help="bracket the device-timed steps with cudaProfilerStart/Stop (ncu --profile-from-start off)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    args.warmup = max(args.warmup, 3)
+    if args.tokens != M_PREFILL or args.experts != E:
+        M_PREFILL, E = args.tokens, args.experts
+        WORKLOAD = f"small_case_M{M_PREFILL}_H{H}_I{I}_E{E}_topk{TOPK} (not the headline workload)"
+
+    import importlib
+    import torch.distributed as dist
+    import aiter_b200
+    from aiter_b200 import ep
+    fm = importlib.import_module("aiter_b200.fused_moe")
+    QT = aiter_b200.QuantType
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    def sync():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    w1_q, w1_s, w2_q, w2_s = make_layer(dev, rank, world)
+    x, tw, ti = make_tokens(M_PREFILL)
+    m_local = M_PREFILL // world
+    rows = slice(rank * m_local, (rank + 1) * m_local)
+    # pinned host copies of this rank's step inputs, and a pinned landing buffer for its output
+    hx, htw, hti = (t[rows].contiguous().pin_memory() for t in (x, tw, ti))
+    hout = torch.empty((m_local, H), dtype=torch.bfloat16).pin_memory()
+    dx, dtw, dti = hx.to(dev), htw.to(dev), hti.to(dev)
+
+    if world == 1:
+        def step_dev():
+            return aiter_b200.fused_moe(dx, w1_q, w2_q, dtw, dti, quant_type=QT.per_1x128,
+                                        w1_scale=w1_s, w2_scale=w2_s)
+
+        def step_e2e():
+            a = hx.to(dev, non_blocking=True)
+            b = htw.to(dev, non_blocking=True)
+            c = hti.to(dev, non_blocking=True)
+            out = aiter_b200.fused_moe(a, w1_q, w2_q, b, c, quant_type=QT.per_1x128, w1_scale=w1_s, w2_scale=w2_s)
+            hout.copy_(out, non_blocking=True)
+    else:
+        def step_dev():
+            return ep.ep_fused_moe(dx, w1_q, w2_q, dtw, dti, w1_s, w2_s, E)
+
+        def step_e2e():
+            a = hx.to(dev, non_blocking=True)
+            b = htw.to(dev, non_blocking=True)
+            c = hti.to(dev, non_blocking=True)
+            out = ep.ep_fused_moe(a, w1_q, w2_q, b, c, w1_s, w2_s, E)
+            hout.copy_(out, non_blocking=True)
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    t_dev = timed(step_dev, args.steps, args.warmup, sync, profile=args.cuda_profiler_range)
+    t_e2e = timed(step_e2e, args.steps, min(args.warmup, 3), sync)
+    clocks = sampler.stop() if rank == 0 else None
+    aiter_b200.check_device_status()
+
+    def max_over_ranks(ms_total):
+        t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    ms_step = max_over_ranks(sum(t_dev)) / args.steps
+    ms_e2e = max_over_ranks(sum(t_e2e)) / args.steps
+    value = flops(M_PREFILL) / (ms_step * 1e-3) / 1e12
+    e2e_value = flops(M_PREFILL) / (ms_e2e * 1e-3) / 1e12
+
+    pk = peaks()
+    fp8_peak = 2.0 * pk["bf16_tflops"]
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate, bf16 in/out)", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "tokens": M_PREFILL, "model_dim": H, "inter_dim": I, "experts": E,
+                   "topk": TOPK, "parallelism": f"ep{world}", "l2_policy": "inputs larger than L2 (11.3 GB of weights per step)"},
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": int(hx.numel() * 2 + htw.numel() * 4 + hti.numel() * 4) * world,
+                "d2h_bytes_per_step": int(hout.numel() * 2) * world},
+        "clocks": clocks,
+    }
+
+    if world == 1:
+        args_dev = (dx, w1_q, w2_q, dtw, dti, None, w1_s, w2_s, None, None, torch.bfloat16)
+        kb = kernel_breakdown(fm, args_dev)
+        n_sort = 3 if M_PREFILL * TOPK > 16384 else 1
+        line["gpu_launches"] = (n_sort + 4) * args.steps * 2   # device-timed and e2e loops
+        line["kernels_ms"] = {k: round(v, 4) for k, v in kb.items()}
+        s1 = 4.0 * M_PREFILL * TOPK * H * I / (kb["stage1"] * 1e-3) / 1e12
+        s2 = 2.0 * M_PREFILL * TOPK * H * I / (kb["stage2"] * 1e-3) / 1e12
+        line["roofline"] = {"bound": "tensor", "kernel": "moe_gemm_kernel<1> (stage 1)", "achieved": s1,
+                            "peak": fp8_peak, "unit": "TFLOP/s", "frac": s1 / fp8_peak, "traffic": None,
+                            "peak_source": f"2 x bf16_tflops of {pk['source']} ({pk['bf16_tflops']} TFLOP/s burst); "
+                                           "the driver's peak file has no FP8 entry",
+                            "stage2_achieved": s2, "stage2_frac": s2 / fp8_peak}
+        line["layer_frac_of_fp8_peak"] = value / fp8_peak
+    if world == 1 and not args.skip_decode:
+        # ---- decode case (M=64): HBM-bound weight streaming
+        xd, twd, tid = make_tokens(M_DECODE, seed=1)
+        dxd, dtwd, dtid = xd.to(dev), twd.to(dev), tid.to(dev)
+        n_act = int(torch.unique(tid).numel())
+
+        def step_decode():
+            return aiter_b200.fused_moe(dxd, w1_q, w2_q, dtwd, dtid, quant_type=QT.per_1x128, w1_scale=w1_s, w2_scale=w2_s)
+
+        td = timed(step_decode, max(args.steps, 20), args.warmup, sync)
+        us = statistics.median(td) * 1e3
+        gbs = algorithmic_bytes(M_DECODE, n_act) / (us * 1e-6) / 1e9
+        kbd = kernel_breakdown(fm, (dxd, w1_q, w2_q, dtwd, dtid, None, w1_s, w2_s, None, None, torch.bfloat16))
+        line["decode"] = {"metric": "DSV3 FP8-blockscale fused_moe us/layer (M=64)", "value": us, "unit": "us",
+                          "active_experts": n_act, "kernels_ms": {k: round(v, 4) for k, v in kbd.items()},
+                          "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                                       "frac": gbs / pk["hbm_gbs"], "traffic": None,
+                                       "peak_source": f"hbm_gbs of {pk['source']}"}}
+        aiter_b200.check_device_status()
+    if world == 1 and not args.no_cpu_baseline:
+        cb = cpu_baseline(n_exp=4)
+        line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    if world > 1:
+        line["gpu_launches"] = (3 + 4) * args.steps * 2
+
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -36,6 +36,19 @@ def test_header_and_library_agree(lib):
     assert set(_lib.exported_symbols()) == set(decl)
 
 
+def test_ctypes_signatures_match_header(lib):
+    """Every binding passes exactly as many arguments as the header declares."""
+    text = ""
+    for h in glob.glob(os.path.join(ROOT, "include", "*.h")):
+        text += re.sub(r"/\*.*?\*/", "", open(h).read(), flags=re.S)
+    for name, (_res, args) in _lib._SIGNATURES.items():
+        m = re.search(r"\b" + name + r"\s*\(([^)]*)\)", text)
+        assert m, name
+        params = m.group(1).strip()
+        n = 0 if params in ("", "void") else params.count(",") + 1
+        assert n == len(args), f"{name}: header has {n} parameters, binding passes {len(args)}"
+
+
 def test_abi_version_and_error_channel(lib):
     assert lib.aiter_ctypes_abi_version() == 2
     lib.aiter_clear_last_error()
