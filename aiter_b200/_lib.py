@@ -15,7 +15,8 @@ import torch
 from .dtypes import AITER_DTYPE
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libaiter_b200.so")
+# AITER_B200_LIB points at a library built elsewhere (same C-ABI); default: the in-tree build
+LIB_PATH = os.environ.get("AITER_B200_LIB") or os.path.join(_HERE, "libaiter_b200.so")
 
 
 class aiter_tensor_t(ctypes.Structure):

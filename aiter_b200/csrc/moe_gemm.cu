@@ -13,7 +13,8 @@
 // Per tile and per 128-wide K block:
 //   warp 0      TMA-loads two [128 rows x 128 B] weight boxes (gate+up rows, or 256 output rows)
 //               into a 128B-swizzled shared-memory stage;
-//   warps 4-7   gather the 128 activation rows of the block (cp.async, 16 B chunks, same swizzle);
+//   warps 4-7   gather the 128 activation rows of the block (cp.async, 16 B chunks, same swizzle)
+//               and the K block's scales; completion is signalled by cp.async.mbarrier.arrive;
 //   warp 1      issues 4 tcgen05.mma (M128 N256 K32, e4m3 -> fp32) into one of two 256-column
 //               TMEM stages, then commits to free the smem stage and to publish the TMEM stage;
 //   warps 8-15  read the TMEM stage (tcgen05.ld) and fold it into fp32 registers with the block
@@ -38,7 +39,6 @@ constexpr int BM = 128;            // sorted rows per tile (== sort unit)
 constexpr int BK = 128;            // K elements (bytes) per pipeline step == scale block
 constexpr int BN = 256;            // UMMA N: 128 gate + 128 up columns, or 256 output columns
 constexpr int kStages = 4;         // shared-memory pipeline depth
-constexpr int kLag = 2;            // cp.async groups a gather thread keeps in flight
 constexpr int kABytes = BM * BK;   // 16 KB
 constexpr int kBBytes = BN * BK;   // 32 KB
 constexpr int kThreads = 512;
@@ -46,6 +46,8 @@ constexpr int kGatherWarp0 = 4;    // warps 4..7
 constexpr int kEpiWarp0 = 8;       // warps 8..15
 constexpr int kEpiThreads = 256;
 constexpr int kTmemCols = 512;     // 2 stages x 256 fp32 columns
+constexpr int kProducerSleepNs = 100;  // back-off of the load roles while no stage is free
+constexpr int kEpilogueSleepNs = 40;   // back-off of the promotion warps while the UMMAs run
 constexpr uint32_t kIdesc = ptx::make_idesc_e4m3_f32(BM, BN);
 
 // shared memory map (offsets from a 1024-byte aligned base)
@@ -56,7 +58,11 @@ constexpr int kNumBars = 2 * kStages + 4;
 constexpr int kOffTmemSlot = kOffBar + kNumBars * 8;
 constexpr int kOffAbort = kOffTmemSlot + 4;
 constexpr int kOffAmax = (kOffAbort + 4 + 15) & ~15;        // float [2 tiles][2 halves][128 rows]
-constexpr int kSmemUsed = kOffAmax + 2 * 2 * BM * 4;
+constexpr int kScaleSlots = 8;                              // ring of per-K-block scales (> kStages + 2)
+constexpr int kOffScaleA = kOffAmax + 2 * 2 * BM * 4;       // float [kScaleSlots][128 rows]
+constexpr int kOffScaleW = kOffScaleA + kScaleSlots * BM * 4;  // float [kScaleSlots][2]
+constexpr int kOffRowTab = kOffScaleW + kScaleSlots * 2 * 4;   // uint32 [2 tiles][128 rows]
+constexpr int kSmemUsed = kOffRowTab + 2 * BM * 4;
 constexpr int kSmemBytes = kSmemUsed + 1024;                // slack for the 1024-byte alignment
 
 struct GemmParams {
@@ -78,9 +84,30 @@ struct GemmParams {
     int* status;
 };
 
+// torch: silu(x) = x / (1 + exp(-x)) in fp32, then * up (aiter/fused_moe.py:3676).
+// The quotient is formed from an approximate reciprocal and one FMA residual correction (error below
+// one fp32 ulp, like the exp it depends on) instead of the ~4x longer IEEE division sequence.
 __device__ __forceinline__ float silu_mul(float g, float u) {
-    // torch: silu(x) = x / (1 + exp(-x)) in fp32, then * up (aiter/fused_moe.py:3676)
-    return __fdiv_rn(g, 1.0f + expf(-g)) * u;
+    if (g < -80.0f) return __fdiv_rn(g, 1.0f + expf(-g)) * u;   // exp(-g) near overflow: exact path
+    const float d = 1.0f + expf(-g);
+    const float y = ptx::rcp_approx(d);
+    const float q = g * y;
+    return fmaf(fmaf(-q, d, g), y, q) * u;
+}
+
+// Correctly rounded a / b given rb = RN(1/b): two FMA residual corrections (the first makes the
+// quotient faithful, the second then rounds it correctly), valid while nothing over- or underflows.
+__device__ __forceinline__ float div_rn_by(float a, float b, float rb) {
+    float q = a * rb;
+    q = fmaf(fmaf(-q, b, a), rb, q);
+    return fmaf(fmaf(-q, b, a), rb, q);
+}
+
+// acc[0..15] += v[0..31] * s with packed fp32x2 FMAs (one instruction per column pair)
+__device__ __forceinline__ void fold32(float2* acc, const uint32_t* v, float2 s) {
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+        acc[j] = __ffma2_rn(make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1])), s, acc[j]);
 }
 
 template <int STAGE>
@@ -98,6 +125,8 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kOffTmemSlot);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffAbort);
     float* amax_x = reinterpret_cast<float*>(smem + kOffAmax);
+    const volatile float* scale_a = reinterpret_cast<const volatile float*>(smem + kOffScaleA);
+    const volatile float* scale_w = reinterpret_cast<const volatile float*>(smem + kOffScaleW);
 
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
     const int lane = threadIdx.x & 31;
@@ -129,15 +158,12 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
     const int total_tiles = (num_valid / BM) * p.n_tiles;
 
     if (warp < kGatherWarp0) {
-        ptx::setmaxnreg_dec<48>();
+        ptx::setmaxnreg_dec<24>();
         if (warp == 0 && lane == 0) {
             // ---------------------------------------------------------------- weight TMA producer
-            uint32_t it = 0;
-            bool ok = true;
-            for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+            auto tile_rows = [&](int t, int& r0, int& r1) {
                 const int blk = t / p.n_tiles, nt = t - blk * p.n_tiles;
                 const int e = p.sorted_eids[blk];
-                int r0, r1;
                 if (STAGE == 1) {
                     r0 = e * p.n_rows + nt * 128;   // gate rows
                     r1 = r0 + p.inter;              // up rows
@@ -145,10 +171,16 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                     r0 = e * p.n_rows + nt * 256;
                     r1 = (nt * 256 + 128 < p.n_rows) ? r0 + 128 : r0;
                 }
+            };
+            uint32_t it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+                int r0, r1;
+                tile_rows(t, r0, r1);
                 for (int kb = 0; kb < p.KB; ++kb, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1u;
-                    if (!(ok = ptx::mbar_wait(empty_bar(s), ph ^ 1u, abort_flag))) break;
+                    if (!(ok = ptx::mbar_wait<kProducerSleepNs>(empty_bar(s), ph ^ 1u, abort_flag))) break;
                     ptx::mbar_arrive_expect_tx(full_bar(s), kBBytes);
                     ptx::tma_load_2d(sB + s * kBBytes, &tmap_w, kb * BK, r0, full_bar(s));
                     ptx::tma_load_2d(sB + s * kBBytes + kBBytes / 2, &tmap_w, kb * BK, r1, full_bar(s));
@@ -166,6 +198,9 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                     const uint32_t tph = (it >> 1) & 1u;
                     if (!(ok = ptx::mbar_wait(tempty_bar(ts), tph ^ 1u, abort_flag))) break;
                     if (!(ok = ptx::mbar_wait(full_bar(s), ph, abort_flag))) break;
+                    // the activation rows were written by cp.async (generic proxy); order them
+                    // before the tensor core's async-proxy reads
+                    ptx::fence_proxy_async();
                     ptx::tc_fence_after();
                     const uint64_t da = ptx::make_kmajor_sw128_desc(sA + s * kABytes);
                     const uint64_t db = ptx::make_kmajor_sw128_desc(sB + s * kBBytes);
@@ -180,50 +215,71 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
         }
     } else if (warp < kEpiWarp0) {
         // -------------------------------------------------------------------- activation gather
-        ptx::setmaxnreg_dec<48>();
-        const int r = threadIdx.x - kGatherWarp0 * 32;   // row of the tile
-        const uint32_t sw = (uint32_t)(r & 7);
+        ptx::setmaxnreg_dec<56>();
+        const int r = threadIdx.x - kGatherWarp0 * 32;   // row whose scale / row offset this thread owns
+        // Copy mapping: 8 consecutive lanes fetch the eight 16-byte chunks of one 128-byte row segment,
+        // so a warp-wide cp.async touches 4 whole cache lines (not 32 partial ones). Pass i of a
+        // thread covers row gw*32 + i*4 + lane/8.
+        const int gw = r >> 5, sub = (r & 31) >> 3;
+        const uint32_t chunk = (uint32_t)(r & 7);
+        uint32_t* row_tab = reinterpret_cast<uint32_t*>(smem + kOffRowTab);   // [2][128] source rows
         uint32_t it = 0;
+        uint32_t tile_par = 0;
         bool ok = true;
-        for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-            const int blk = t / p.n_tiles;
+        for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, tile_par ^= 1u) {
+            const int blk = t / p.n_tiles, nt = t - blk * p.n_tiles;
             const int prow = blk * BM + r;
-            const uint8_t* src;
-            uint32_t nbytes = 16;
+            uint32_t my_row;                 // source row of tile row r, or 0xFFFFFFFF for padding
             if (STAGE == 1) {
                 const int tok = p.sorted_ids[prow] & 0xFFFFFF;
-                const bool valid = tok < tokens;
-                src = p.a + (size_t)(valid ? tok : 0) * p.K;
-                nbytes = valid ? 16u : 0u;   // pads: zero-filled rows
+                my_row = tok < tokens ? (uint32_t)tok : 0xFFFFFFFFu;
             } else {
-                src = p.a + (size_t)prow * p.K;
+                my_row = (uint32_t)prow;
+            }
+            const bool my_valid = my_row != 0xFFFFFFFFu;
+            const float* as_src = p.a_scale + (size_t)(my_valid ? my_row : 0u) * p.KB;
+            row_tab[tile_par * BM + r] = my_row;
+            ptx::named_barrier(2, BM);       // the 128 gather threads; table of the previous tile is
+                                             // untouched (other parity), so one barrier per tile suffices
+            const uint8_t* src[8];
+            uint32_t nbytes[8], dst_off[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int row = gw * 32 + i * 4 + sub;
+                const uint32_t sr = row_tab[tile_par * BM + row];
+                nbytes[i] = sr != 0xFFFFFFFFu ? 16u : 0u;   // pads: zero-filled rows
+                src[i] = p.a + (size_t)(nbytes[i] ? sr : 0u) * p.K + chunk * 16;
+                dst_off[i] = (uint32_t)row * BK + ((chunk ^ (uint32_t)(row & 7)) << 4);
+            }
+            // threads 0 and 1 also fetch the two weight-block scales of this tile
+            const float* ws_src = p.w_scale;
+            if (r < 2) {
+                const int e = p.sorted_eids[blk];
+                int nb;
+                if (STAGE == 1) nb = (r == 0) ? nt : p.inter / 128 + nt;
+                else nb = (r == 0) ? nt * 2 : min(nt * 2 + 1, p.n_rows / 128 - 1);
+                ws_src = p.w_scale + ((size_t)e * (p.n_rows / 128) + nb) * p.KB;
             }
             for (int kb = 0; kb < p.KB; ++kb, ++it) {
                 const int s = it % kStages;
                 const uint32_t ph = (it / kStages) & 1u;
-                if (!(ok = ptx::mbar_wait(empty_bar(s), ph ^ 1u, abort_flag))) break;
-                const uint32_t dst = sA + s * kABytes + r * BK;
-                const uint8_t* g = src + (size_t)kb * BK;
+                if (!(ok = ptx::mbar_wait<kProducerSleepNs>(empty_bar(s), ph ^ 1u, abort_flag))) break;
+                const uint32_t dst = sA + s * kABytes;
 #pragma unroll
-                for (uint32_t c = 0; c < 8; ++c) ptx::cp_async16(dst + ((c ^ sw) << 4), g + c * 16, nbytes);
-                ptx::cp_async_commit();
-                if (it >= (uint32_t)kLag) {
-                    ptx::cp_async_wait<kLag>();
-                    ptx::fence_proxy_async();
-                    ptx::mbar_arrive(full_bar((it - kLag) % kStages));
-                }
+                for (int i = 0; i < 8; ++i) ptx::cp_async16(dst + dst_off[i], src[i] + (size_t)kb * BK, nbytes[i]);
+                const uint32_t slot = it % kScaleSlots;
+                ptx::cp_async4(sbase + kOffScaleA + (slot * BM + r) * 4, as_src + kb, my_valid ? 4u : 0u);
+                if (r < 2) ptx::cp_async4(sbase + kOffScaleW + (slot * 2 + r) * 4, ws_src + kb, 4u);
+                // the arrival is delivered by the copy engine when this thread's copies have landed,
+                // so the thread can go on to the next stage at once (all kStages stay in flight)
+                ptx::cp_async_mbar_arrive(full_bar(s));
             }
         }
-        // drain: the last kLag steps still owe their arrival
-        ptx::cp_async_wait<0>();
-        ptx::fence_proxy_async();
-        if (ok) {
-            for (uint32_t j = (it > (uint32_t)kLag ? it - kLag : 0u); j < it; ++j)
-                ptx::mbar_arrive(full_bar(j % kStages));
-        }
+        ptx::cp_async_commit();
+        ptx::cp_async_wait<0>();   // nothing of this thread is in flight when the CTA winds down
     } else {
         // -------------------------------------------------------------------- promotion + epilogue
-        ptx::setmaxnreg_inc<208>();
+        ptx::setmaxnreg_inc<216>();
         const int q = warp & 3;                         // TMEM lane quarter this warp may read
         const int half = (warp - kEpiWarp0) >> 2;       // which 64 columns of each 128-column group
         const int r = q * 32 + lane;                    // row of the tile == TMEM lane
@@ -233,52 +289,47 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
         bool ok = true;
         for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, tile_par ^= 1u) {
             const int blk = t / p.n_tiles, nt = t - blk * p.n_tiles;
-            const int e = p.sorted_eids[blk];
             const int prow = blk * BM + r;
             const int tok = p.sorted_ids[prow] & 0xFFFFFF;
             const bool valid = tok < tokens;
-            const float* as_row;
-            int nb0, nb1;
-            if (STAGE == 1) {
-                as_row = p.a_scale + (size_t)(valid ? tok : 0) * p.KB;
-                nb0 = nt;
-                nb1 = p.inter / 128 + nt;
-            } else {
-                as_row = p.a_scale + (size_t)prow * p.KB;
-                nb0 = nt * 2;
-                nb1 = min(nt * 2 + 1, p.n_rows / 128 - 1);
-            }
-            const float* ws0 = p.w_scale + ((size_t)e * (p.n_rows / 128) + nb0) * p.KB;
-            const float* ws1 = p.w_scale + ((size_t)e * (p.n_rows / 128) + nb1) * p.KB;
+            // a warp whose 32 rows are all padding (decode: most of them) leaves its accumulators at 0
+            const bool warp_live = __any_sync(0xffffffffu, valid);
 
-            float acc[128];
+            // acc[j] holds columns (2j, 2j+1) of this thread's first 64 columns for j < 32 and of
+            // its second 64 columns (the other 128-column group) for j >= 32
+            float2 acc[64];
 #pragma unroll
-            for (int j = 0; j < 128; ++j) acc[j] = 0.f;
+            for (int j = 0; j < 64; ++j) acc[j] = make_float2(0.f, 0.f);
 
             for (int kb = 0; kb < p.KB; ++kb, ++it) {
                 const int ts = it & 1;
                 const uint32_t tph = (it >> 1) & 1u;
-                const float sa = (STAGE == 2 || valid) ? __ldg(as_row + kb) : 0.f;
-                const float s0 = sa * __ldg(ws0 + kb);
-                const float s1 = sa * __ldg(ws1 + kb);
-                if (!(ok = ptx::mbar_wait(tfull_bar(ts), tph, abort_flag))) break;
+                if (!(ok = ptx::mbar_wait<kEpilogueSleepNs>(tfull_bar(ts), tph, abort_flag))) break;
                 ptx::tc_fence_after();
+                const uint32_t slot = it % kScaleSlots;
+                const float sa = scale_a[slot * BM + r];
+                const float s0 = sa * scale_w[slot * 2], s1 = sa * scale_w[slot * 2 + 1];
+                const float2 s0v = make_float2(s0, s0), s1v = make_float2(s1, s1);
                 const uint32_t ta = lane_addr + ts * BN + half * 64;
-                uint32_t v[64];
-                ptx::tmem_ld_x32(ta, v);
-                ptx::tmem_ld_x32(ta + 32, v + 32);
-                ptx::tmem_ld_wait();
-#pragma unroll
-                for (int j = 0; j < 64; ++j) acc[j] = fmaf(__uint_as_float(v[j]), s0, acc[j]);
-                ptx::tmem_ld_x32(ta + 128, v);
-                ptx::tmem_ld_x32(ta + 160, v + 32);
-                ptx::tmem_ld_wait();
+                // Four 32-column chunks: load + wait, then 16 packed FMAs.  The packed fp32x2 FMAs matter:
+                // they need half the issue slots of scalar FMAs, and with scalar FMAs the two promotion
+                // warps that share a scheduler with the UMMA-issuing warp starve it (measured: the UMMA
+                // rate halves).
+                uint32_t v[32];
+                if (warp_live) {
+                    ptx::tmem_ld_x32_sync(ta, v);
+                    fold32(acc, v, s0v);
+                    ptx::tmem_ld_x32_sync(ta + 32, v);
+                    fold32(acc + 16, v, s0v);
+                    ptx::tmem_ld_x32_sync(ta + 128, v);
+                    fold32(acc + 32, v, s1v);
+                    ptx::tmem_ld_x32_sync(ta + 160, v);
+                }
                 // all reads of this TMEM stage are done: hand it back to the MMA warp
                 ptx::tc_fence_before();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(tempty_bar(ts));
-#pragma unroll
-                for (int j = 0; j < 64; ++j) acc[64 + j] = fmaf(__uint_as_float(v[j]), s1, acc[64 + j]);
+                if (warp_live) fold32(acc + 48, v, s1v);
             }
             if (!ok) break;
 
@@ -287,10 +338,11 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                 // aiter/fused_moe.py:3668-3681 then aiter/ops/quant.py:64-94 on the bf16 values.
                 float amax = 0.f;
 #pragma unroll
-                for (int j = 0; j < 64; ++j) {
-                    float h = __bfloat162float(__float2bfloat16_rn(silu_mul(acc[j], acc[64 + j])));
-                    acc[j] = h;
-                    amax = fmaxf(amax, fabsf(h));
+                for (int j = 0; j < 32; ++j) {   // acc[j] is overwritten by the two activations it feeds
+                    float h0 = __bfloat162float(__float2bfloat16_rn(silu_mul(acc[j].x, acc[32 + j].x)));
+                    float h1 = __bfloat162float(__float2bfloat16_rn(silu_mul(acc[j].y, acc[32 + j].y)));
+                    acc[j] = make_float2(h0, h1);
+                    amax = fmaxf(amax, fmaxf(fabsf(h0), fabsf(h1)));
                 }
                 float* ax = amax_x + tile_par * (2 * BM);
                 ax[half * BM + r] = amax;
@@ -299,13 +351,26 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                 float scale = __fdiv_rn(amax, 448.0f);
                 if (scale == 0.f) scale = 1.f;
                 uint32_t w[16];
+                if (scale > 1e-30f) {
+                    // x / scale, correctly rounded, from one exact reciprocal per row
+                    const float rs = __frcp_rn(scale);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    float2 lo = make_float2(__fdiv_rn(acc[4 * j], scale), __fdiv_rn(acc[4 * j + 1], scale));
-                    float2 hi = make_float2(__fdiv_rn(acc[4 * j + 2], scale), __fdiv_rn(acc[4 * j + 3], scale));
-                    uint32_t a = __nv_cvt_float2_to_fp8x2(lo, __NV_SATFINITE, __NV_E4M3);
-                    uint32_t b = __nv_cvt_float2_to_fp8x2(hi, __NV_SATFINITE, __NV_E4M3);
-                    w[j] = a | (b << 16);
+                    for (int j = 0; j < 16; ++j) {
+                        float2 lo = make_float2(div_rn_by(acc[2 * j].x, scale, rs), div_rn_by(acc[2 * j].y, scale, rs));
+                        float2 hi = make_float2(div_rn_by(acc[2 * j + 1].x, scale, rs), div_rn_by(acc[2 * j + 1].y, scale, rs));
+                        uint32_t a = __nv_cvt_float2_to_fp8x2(lo, __NV_SATFINITE, __NV_E4M3);
+                        uint32_t b = __nv_cvt_float2_to_fp8x2(hi, __NV_SATFINITE, __NV_E4M3);
+                        w[j] = a | (b << 16);
+                    }
+                } else {   // subnormal-range scale: the reciprocal would overflow
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        float2 lo = make_float2(__fdiv_rn(acc[2 * j].x, scale), __fdiv_rn(acc[2 * j].y, scale));
+                        float2 hi = make_float2(__fdiv_rn(acc[2 * j + 1].x, scale), __fdiv_rn(acc[2 * j + 1].y, scale));
+                        uint32_t a = __nv_cvt_float2_to_fp8x2(lo, __NV_SATFINITE, __NV_E4M3);
+                        uint32_t b = __nv_cvt_float2_to_fp8x2(hi, __NV_SATFINITE, __NV_E4M3);
+                        w[j] = a | (b << 16);
+                    }
                 }
                 uint4* dst = reinterpret_cast<uint4*>(p.a2 + (size_t)prow * p.inter + nt * 128 + half * 64);
 #pragma unroll
@@ -318,13 +383,13 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                     const int H = p.n_rows;
                     float* dst = p.acc + (size_t)tok * H + nt * 256 + half * 64;
 #pragma unroll
-                    for (int j = 0; j < 64; j += 4)
-                        ptx::red_add_v4(dst + j, wgt * acc[j], wgt * acc[j + 1], wgt * acc[j + 2], wgt * acc[j + 3]);
+                    for (int j = 0; j < 32; j += 2)
+                        ptx::red_add_v4(dst + 2 * j, wgt * acc[j].x, wgt * acc[j].y, wgt * acc[j + 1].x, wgt * acc[j + 1].y);
                     if (nt * 256 + 128 < H) {
 #pragma unroll
-                        for (int j = 0; j < 64; j += 4)
-                            ptx::red_add_v4(dst + 128 + j, wgt * acc[64 + j], wgt * acc[65 + j],
-                                            wgt * acc[66 + j], wgt * acc[67 + j]);
+                        for (int j = 0; j < 32; j += 2)
+                            ptx::red_add_v4(dst + 128 + 2 * j, wgt * acc[32 + j].x, wgt * acc[32 + j].y,
+                                            wgt * acc[33 + j].x, wgt * acc[33 + j].y);
                     }
                 }
             }

@@ -47,11 +47,15 @@ constexpr long long kWaitLimitCycles = 4000000000LL;  // about 2 s at 1.9 GHz
 // Returns false if the wait ran out.  A waiter gives up only on its own clock, never because
 // another thread did: all waiters of one barrier phase then take the same way out, which keeps
 // thread groups that later meet at a hardware barrier together.
+// SLEEP_NS > 0 backs off with nanosleep between polls: a polling warp otherwise takes issue
+// slots from the warps of its SM sub-partition that do the arithmetic.
+template <int SLEEP_NS = 0>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
+        if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
         if ((++spins & 0xffu) == 0 && clock64() - t0 > kWaitLimitCycles) {
             *abort_flag = 1;
             return false;
@@ -79,6 +83,16 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* m, 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
                  : "memory");
+}
+// 4-byte copy (src_bytes = 0 writes a zero).
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
+                 : "memory");
+}
+// mbarrier arrival that fires once every cp.async this thread has issued so far has landed;
+// it counts as one of the barrier's expected arrivals.
+__device__ __forceinline__ void cp_async_mbar_arrive(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
@@ -122,9 +136,6 @@ __device__ __forceinline__ void tc_fence_before() {
 __device__ __forceinline__ void tc_fence_after() {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
-__device__ __forceinline__ void tmem_ld_wait() {
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
 
 // D[tmem] (+)= A[smem] * B[smem], e4m3 x e4m3 -> fp32, one CTA.  Issued by ONE thread.
 __device__ __forceinline__ void umma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
@@ -159,12 +170,15 @@ __host__ __device__ constexpr uint32_t make_idesc_e4m3_f32(int m, int n) {
     return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-// 32 consecutive fp32 columns of this thread's TMEM lane.
-__device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t* r) {
+// 32 consecutive fp32 columns of this thread's TMEM lane, loaded AND waited for in one asm
+// statement: the registers are valid when the statement ends, so the compiler cannot schedule a
+// consumer between the asynchronous load and its tcgen05.wait::ld.
+__device__ __forceinline__ void tmem_ld_x32_sync(uint32_t taddr, uint32_t* r) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+        "tcgen05.wait::ld.sync.aligned;"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
           "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
           "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
@@ -172,6 +186,12 @@ __device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t* r) {
           "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
         : "memory");
+}
+
+__device__ __forceinline__ float rcp_approx(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 
 // Vector fp32 reduction into global memory (one 16-byte L2 atomic).

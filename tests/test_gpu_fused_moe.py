@@ -176,7 +176,7 @@ def test_dsv3_prefill_sampled_tokens():
     out2 = run(c2)
     # fp32 reductions land in a different order on every run: isolated last-bit flips only
     s = moe_oracle.error_stats(out2, (out.float() * 2).to(torch.bfloat16))
-    assert s["n_diff"] <= 1e-3 * s["numel"] and s["max_abs_over_rms"] <= 0.01, s
+    assert s["n_diff"] <= 1e-3 * s["numel"] and s["max_abs_over_rms"] <= 0.02, s
 
 
 def test_bad_shapes_raise():
