@@ -46,6 +46,7 @@ constexpr int kGatherWarp0 = 4;    // warps 4..7
 constexpr int kEpiWarp0 = 8;       // warps 8..15
 constexpr int kEpiThreads = 256;
 constexpr int kTmemCols = 512;     // 2 stages x 256 fp32 columns
+constexpr int kTmaSleepNs = 0;         // the single TMA thread polls without back-off
 constexpr int kProducerSleepNs = 100;  // back-off of the load roles while no stage is free
 constexpr int kEpilogueSleepNs = 40;   // back-off of the promotion warps while the UMMAs run
 constexpr uint32_t kIdesc = ptx::make_idesc_e4m3_f32(BM, BN);
@@ -62,7 +63,9 @@ constexpr int kScaleSlots = 8;                              // ring of per-K-blo
 constexpr int kOffScaleA = kOffAmax + 2 * 2 * BM * 4;       // float [kScaleSlots][128 rows]
 constexpr int kOffScaleW = kOffScaleA + kScaleSlots * BM * 4;  // float [kScaleSlots][2]
 constexpr int kOffRowTab = kOffScaleW + kScaleSlots * 2 * 4;   // uint32 [2 tiles][128 rows]
-constexpr int kSmemUsed = kOffRowTab + 2 * BM * 4;
+constexpr int kStageRow = 20;                                  // floats per staged row: 16 + 4 of padding
+constexpr int kOffStage = kOffRowTab + 2 * BM * 4;             // float [8 warps][32 rows][kStageRow] (stage 2)
+constexpr int kSmemUsed = kOffStage + 8 * 32 * kStageRow * 4;
 constexpr int kSmemBytes = kSmemUsed + 1024;                // slack for the 1024-byte alignment
 
 struct GemmParams {
@@ -180,7 +183,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                 for (int kb = 0; kb < p.KB; ++kb, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1u;
-                    if (!(ok = ptx::mbar_wait<kProducerSleepNs>(empty_bar(s), ph ^ 1u, abort_flag))) break;
+                    if (!(ok = ptx::mbar_wait<kTmaSleepNs>(empty_bar(s), ph ^ 1u, abort_flag))) break;
                     ptx::mbar_arrive_expect_tx(full_bar(s), kBBytes);
                     ptx::tma_load_2d(sB + s * kBBytes, &tmap_w, kb * BK, r0, full_bar(s));
                     ptx::tma_load_2d(sB + s * kBBytes + kBBytes / 2, &tmap_w, kb * BK, r1, full_bar(s));
@@ -377,19 +380,38 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                 for (int j = 0; j < 4; ++j) dst[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
                 if (half == 0) p.a2_scale[(size_t)prow * (p.inter / 128) + nt] = scale;
             } else {
-                // out[token] += weight * row  (aiter/fused_moe.py:3802-3811); fp32 L2 reductions
-                if (valid) {
-                    const float wgt = p.sorted_w[prow];
-                    const int H = p.n_rows;
-                    float* dst = p.acc + (size_t)tok * H + nt * 256 + half * 64;
+                // out[token] += weight * row  (aiter/fused_moe.py:3802-3811) as fp32 L2 reductions.
+                // A thread holds one row, so reductions issued straight from registers would hit 32
+                // different rows per instruction (16 B each).  Each warp instead passes 16-column
+                // chunks through a padded shared-memory buffer and re-reads them with 4 lanes per row:
+                // one instruction then covers 8 rows x 64 contiguous bytes.
+                const float wgt = valid ? p.sorted_w[prow] : 0.f;
+                const int my_tok = valid ? tok : -1;
+                const int H = p.n_rows;
+                float* sbuf = reinterpret_cast<float*>(smem + kOffStage) + (warp - kEpiWarp0) * (32 * kStageRow);
+                const bool warp_valid = __any_sync(0xffffffffu, valid);
+                const int n_chunks = (nt * 256 + 128 < H) ? 8 : 4;
+                if (warp_valid) {
 #pragma unroll
-                    for (int j = 0; j < 32; j += 2)
-                        ptx::red_add_v4(dst + 2 * j, wgt * acc[j].x, wgt * acc[j].y, wgt * acc[j + 1].x, wgt * acc[j + 1].y);
-                    if (nt * 256 + 128 < H) {
+                    for (int c = 0; c < 8; ++c) {
+                        if (c < n_chunks) {
+                            const int a0 = (c < 4) ? c * 8 : 32 + (c - 4) * 8;   // first float2 of the chunk
+                            const int col0 = nt * 256 + ((c < 4) ? 0 : 128) + half * 64 + (c & 3) * 16;
+                            float4* wr = reinterpret_cast<float4*>(sbuf + lane * kStageRow);
 #pragma unroll
-                        for (int j = 0; j < 32; j += 2)
-                            ptx::red_add_v4(dst + 128 + 2 * j, wgt * acc[32 + j].x, wgt * acc[32 + j].y,
-                                            wgt * acc[33 + j].x, wgt * acc[33 + j].y);
+                            for (int j = 0; j < 4; ++j)
+                                wr[j] = make_float4(wgt * acc[a0 + 2 * j].x, wgt * acc[a0 + 2 * j].y,
+                                                    wgt * acc[a0 + 2 * j + 1].x, wgt * acc[a0 + 2 * j + 1].y);
+                            __syncwarp();
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int idx = i * 32 + lane, rr = idx >> 2, c4 = idx & 3;
+                                const float4 v = *reinterpret_cast<const float4*>(sbuf + rr * kStageRow + c4 * 4);
+                                const int tk = __shfl_sync(0xffffffffu, my_tok, rr);
+                                if (tk >= 0) ptx::red_add_v4(p.acc + (size_t)tk * H + col0 + c4 * 4, v.x, v.y, v.z, v.w);
+                            }
+                            __syncwarp();
+                        }
                     }
                 }
             }
