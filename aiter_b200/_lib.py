@@ -41,6 +41,8 @@ _SIGNATURES = {
     "b200_moe_sorting_get_workspace_size": (ctypes.c_int64, [ctypes.c_int] * 3),
     "b200_moe_sorting_fwd": (ctypes.c_int, [_T] * 7 + [ctypes.c_int, ctypes.c_int, _T, _T, _T,
                                                 ctypes.c_int, _T, ctypes.c_void_p]),
+    "b200_moe_sorting_fwd_noalloc": (ctypes.c_int, [_T] * 7 + [ctypes.c_int, ctypes.c_int, _T, _T, _T,
+                                                        ctypes.c_void_p]),
     "b200_moe_quant_1x128": (ctypes.c_int, [_T] * 3 + [ctypes.c_void_p]),
     "b200_moe_stage1": (ctypes.c_int, [_T] * 10 + [ctypes.c_void_p]),
     "b200_moe_stage2": (ctypes.c_int, [_T] * 10 + [ctypes.c_void_p]),

@@ -18,6 +18,9 @@ int64_t sorting_workspace_bytes(int tokens, int num_experts, int topk);
 void launch_moe_sorting(const aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*,
                         aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*, int, int, const aiter_tensor_t*,
                         const aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*, cudaStream_t);
+void launch_moe_sorting_noalloc(const aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*,
+                                aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*, int, int, const aiter_tensor_t*,
+                                const aiter_tensor_t*, aiter_tensor_t*, cudaStream_t);
 void launch_quant_1x128(aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*, cudaStream_t);
 void launch_moe_stage1(const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*,
                        const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*,
@@ -100,6 +103,27 @@ B200_EXPORT int b200_moe_sorting_fwd(const aiter_tensor_t* topk_ids, const aiter
         launch_moe_sorting(topk_ids, topk_weights, sorted_token_ids, sorted_weights, sorted_expert_ids,
                            num_valid_ids, moe_buf, num_experts, unit_size, local_expert_mask, num_local_tokens,
                            workspace, local_topk_ids, (cudaStream_t)stream);
+    });
+}
+
+// The sort for callers that cannot provide a workspace (see moe_sorting.cu): same outputs as
+// b200_moe_sorting_fwd, scratch taken from a fixed array inside the library.  The first call on a
+// device looks up the array's device address (cudaGetSymbolAddress) and should therefore happen
+// before any stream capture; later calls only launch kernels.  All calls on one device share the
+// array, so two of them must not overlap on the GPU (different streams without ordering would race).
+B200_EXPORT int b200_moe_sorting_fwd_noalloc(const aiter_tensor_t* topk_ids, const aiter_tensor_t* topk_weights,
+                                             aiter_tensor_t* sorted_token_ids, aiter_tensor_t* sorted_weights,
+                                             aiter_tensor_t* sorted_expert_ids, aiter_tensor_t* num_valid_ids,
+                                             aiter_tensor_t* moe_buf, int num_experts, int unit_size,
+                                             const aiter_tensor_t* local_expert_mask,
+                                             const aiter_tensor_t* num_local_tokens, aiter_tensor_t* local_topk_ids,
+                                             void* stream) {
+    return safe_call([&] {
+        B200_CHECK(topk_ids != nullptr, "topk_ids must not be NULL");
+        DeviceGuard g(topk_ids->device_id);
+        launch_moe_sorting_noalloc(topk_ids, topk_weights, sorted_token_ids, sorted_weights, sorted_expert_ids,
+                                   num_valid_ids, moe_buf, num_experts, unit_size, local_expert_mask,
+                                   num_local_tokens, local_topk_ids, (cudaStream_t)stream);
     });
 }
 

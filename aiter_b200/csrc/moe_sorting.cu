@@ -404,4 +404,62 @@ void launch_moe_sorting(const aiter_tensor_t* topk_ids, const aiter_tensor_t* to
     B200_CUDA(cudaGetLastError());
 }
 
+// ------------------------------------------------------------------------------------------------
+// Sorting without any allocation by anybody.
+//
+// Some callers have no way to hand over a workspace: a host runtime that reaches this library over
+// an FFI and owns no device allocator of its own, a serving loop whose memory pool is frozen after
+// start-up, or code that must not trigger the implicit device synchronisation of cudaMalloc/cudaFree
+// in the middle of its steady state.  For them the multi-CTA sort keeps its per-chunk counters in a
+// fixed array that is part of the loaded module.  Every GPU that loads the library holds these
+// kStaticScratchInts * 4 bytes until the process exits.
+//
+// The name g_sort_scratch is only a host-side handle: the kernels get the real device address from
+// cudaGetSymbolAddress, looked up once per device with that device current.
+constexpr int kStaticMaxChunks = 64;                       // 64 chunks x 4096 routes = 262144 routes
+constexpr int kStaticScratchInts = kStaticMaxChunks * kMaxExperts + kMaxExperts;   // 260 KiB
+static __device__ __align__(256) int g_sort_scratch[kStaticScratchInts];
+
+int64_t static_scratch_bytes() { return (int64_t)kStaticScratchInts * (int64_t)sizeof(int); }
+
+// Device address of the scratch array on `dev` (which must be the current device).
+static int* static_scratch_ptr(int dev) {
+    static int* cached[64] = {nullptr};
+    if (dev >= 0 && dev < 64 && cached[dev]) return cached[dev];
+    void* ptr = nullptr;
+    B200_CUDA(cudaGetSymbolAddress(&ptr, g_sort_scratch));
+    B200_CHECK(ptr != nullptr, "cudaGetSymbolAddress returned a null scratch address");
+    if (dev >= 0 && dev < 64) cached[dev] = (int*)ptr;
+    return (int*)ptr;
+}
+
+void launch_moe_sorting_noalloc(const aiter_tensor_t* topk_ids, const aiter_tensor_t* topk_weights,
+                                aiter_tensor_t* sorted_ids, aiter_tensor_t* sorted_w,
+                                aiter_tensor_t* sorted_eids, aiter_tensor_t* num_valid,
+                                aiter_tensor_t* moe_buf, int E, int unit, const aiter_tensor_t* mask,
+                                const aiter_tensor_t* num_local, aiter_tensor_t* local_topk_ids,
+                                cudaStream_t stream) {
+    check_tensor(topk_ids, "topk_ids", AITER_DTYPE_i32, 2);
+    const int64_t M = topk_ids->shape[0], topk = topk_ids->shape[1];
+    B200_CHECK(E >= 1 && E <= kMaxExperts, "num_experts must be in [1, ", kMaxExperts, "], got ", E);
+    const int64_t need = sorting_workspace_bytes((int)M, E, (int)topk);
+    // stated limit: 262144 routes (tokens*topk); with that and E <= 1024 the scratch always suffices
+    B200_CHECK(M * topk <= (int64_t)kStaticMaxChunks * kChunk && need <= static_scratch_bytes(),
+               "problem too large for the built-in scratch: ", M * topk, " routes (tokens*topk), the limit is ",
+               (int64_t)kStaticMaxChunks * kChunk, " with up to ", kMaxExperts, " experts (", static_scratch_bytes(),
+               " bytes held by the library); use b200_moe_sorting_fwd with a caller-provided workspace instead");
+    // Nothing in the scratch has to start at zero: the count kernel writes every counter it covers
+    // and the scan kernel every base before anything reads them.
+    aiter_tensor_t ws{};
+    ws.ptr = static_scratch_ptr(topk_ids->device_id);
+    ws.numel_ = (size_t)static_scratch_bytes();
+    ws.ndim = 1;
+    ws.shape[0] = (int64_t)ws.numel_;
+    ws.strides[0] = 1;
+    ws.dtype_ = AITER_DTYPE_u8;
+    ws.device_id = topk_ids->device_id;
+    launch_moe_sorting(topk_ids, topk_weights, sorted_ids, sorted_w, sorted_eids, num_valid, moe_buf, E, unit,
+                       mask, num_local, need > 0 ? &ws : nullptr, local_topk_ids, stream);
+}
+
 }  // namespace b200

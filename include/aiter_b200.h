@@ -83,6 +83,23 @@ int b200_moe_sorting_fwd(const aiter_tensor_t* topk_ids, const aiter_tensor_t* t
                          const aiter_tensor_t* num_local_tokens, aiter_tensor_t* workspace,
                          int dispatch_policy, aiter_tensor_t* local_topk_ids, void* stream);
 
+/* No counterpart in the reference.  The same sort for callers that cannot allocate or pass a
+ * workspace: a host runtime bound over an FFI that owns no device allocator, a serving loop whose
+ * pool is frozen after start-up, or code that must avoid the device-wide synchronisation a
+ * cudaMalloc/cudaFree implies.  The scratch lives in a fixed array inside the library
+ * (266240 bytes, held by every GPU that loads it); problems that
+ * need more (tokens*topk > 262144 routes) are rejected with an error.  Arguments as for
+ * b200_moe_sorting_fwd without workspace and dispatch_policy.  The first call on a device resolves
+ * the array's device address and should precede any stream capture.  Calls on the same device share
+ * the array: do not let two of them overlap on the GPU. */
+int b200_moe_sorting_fwd_noalloc(const aiter_tensor_t* topk_ids, const aiter_tensor_t* topk_weights,
+                                 aiter_tensor_t* sorted_token_ids, aiter_tensor_t* sorted_weights,
+                                 aiter_tensor_t* sorted_expert_ids, aiter_tensor_t* num_valid_ids,
+                                 aiter_tensor_t* moe_buf, int num_experts, int unit_size,
+                                 const aiter_tensor_t* local_expert_mask,
+                                 const aiter_tensor_t* num_local_tokens, aiter_tensor_t* local_topk_ids,
+                                 void* stream);
+
 /* Dynamic per-row, per-128-column FP8 e4m3 quantisation: scale = amax/448 (1 when amax is 0),
  * codes = RNE(x / scale).  Replaces dynamic_per_token_scaled_quant with group_size=128
  * (aiter/ops/quant.py:439-483, csrc/kernels/quant_kernels.cu:27-167,720-830) with the
