@@ -24,7 +24,7 @@ import torch
 import torch.distributed as dist
 
 from . import _lib, dtypes
-from .fused_moe import fused_moe_stages, per_group_quant_hip
+from .fused_moe import _mark, fused_moe_stages, per_group_quant_hip
 
 
 def expert_mask_for_rank(num_experts: int, rank: int, world: int, device=None) -> torch.Tensor:
@@ -37,11 +37,10 @@ def expert_mask_for_rank(num_experts: int, rank: int, world: int, device=None) -
     return mask
 
 
-def _gpu_local_layer(a1, a1_scale, w1, w2, topk_weight, topk_ids, expert_mask, w1_scale, w2_scale):
+def _gpu_local_layer(a1, a1_scale, w1, w2, topk_weight, topk_ids, expert_mask, w1_scale, w2_scale, timers=None):
     """All rows, local experts -> fp32 partial [M, H] (no final rounding)."""
-    _, inter = fused_moe_stages(a1, w1, w2, topk_weight, topk_ids, expert_mask, w1_scale, w2_scale,
-                                   a1_scale, None, dtypes.bf16, return_intermediates=True)
-    return inter["acc"]
+    return fused_moe_stages(a1, w1, w2, topk_weight, topk_ids, expert_mask, w1_scale, w2_scale,
+                            a1_scale, None, None, timers=timers)
 
 
 def _gpu_quant(x):
@@ -56,7 +55,7 @@ def _gpu_finalize(acc, dtype):
 
 def ep_fused_moe(x_local, w1_local, w2_local, topk_weight_local, topk_ids_local, w1_scale_local,
                  w2_scale_local, num_experts, group=None, dtype=torch.bfloat16,
-                 quant=_gpu_quant, local_layer=_gpu_local_layer, finalize=_gpu_finalize):
+                 quant=_gpu_quant, local_layer=_gpu_local_layer, finalize=_gpu_finalize, timers=None):
     """x_local [M/G, H] bf16, routing [M/G, topk] with GLOBAL expert ids -> out [M/G, H].
 
     Every rank must pass the same number of rows."""
@@ -65,24 +64,38 @@ def ep_fused_moe(x_local, w1_local, w2_local, topk_weight_local, topk_ids_local,
     m_local, H = x_local.shape
     topk = topk_ids_local.shape[1]
     dev = x_local.device
+    _mark(timers, "ep_quant")
     a1_l, a1s_l = quant(x_local)
+    _mark(timers, "ep_all_gather")
     if world == 1:
         a1, a1s, ids, wts = a1_l, a1s_l, topk_ids_local, topk_weight_local
     else:
+        # two collectives: the codes, and one int32 side buffer per row with scales, ids and weights
+        kb = a1s_l.shape[1]
+        side_l = torch.cat([a1s_l.view(torch.int32), topk_ids_local.view(torch.int32),
+                            topk_weight_local.contiguous().view(torch.int32)], dim=1)
         a1 = torch.empty((world * m_local, H), dtype=torch.uint8, device=dev)
-        a1s = torch.empty((world * m_local, H // 128), dtype=torch.float32, device=dev)
-        ids = torch.empty((world * m_local, topk), dtype=torch.int32, device=dev)
-        wts = torch.empty((world * m_local, topk), dtype=torch.float32, device=dev)
+        side = torch.empty((world * m_local, side_l.shape[1]), dtype=torch.int32, device=dev)
         dist.all_gather_into_tensor(a1, a1_l.view(torch.uint8), group=group)
-        dist.all_gather_into_tensor(a1s, a1s_l.contiguous(), group=group)
-        dist.all_gather_into_tensor(ids, topk_ids_local.contiguous(), group=group)
-        dist.all_gather_into_tensor(wts, topk_weight_local.contiguous(), group=group)
+        dist.all_gather_into_tensor(side, side_l, group=group)
         a1 = a1.view(torch.float8_e4m3fn)
+        a1s = side[:, :kb].contiguous().view(torch.float32)
+        ids = side[:, kb:kb + topk].contiguous()
+        wts = side[:, kb + topk:].contiguous().view(torch.float32)
     mask = expert_mask_for_rank(num_experts, rank, world, device=dev)
-    partial = local_layer(a1, a1s, w1_local, w2_local, wts, ids, mask, w1_scale_local, w2_scale_local)
+    if timers is not None:
+        partial = local_layer(a1, a1s, w1_local, w2_local, wts, ids, mask, w1_scale_local, w2_scale_local,
+                              timers=timers)
+        timers.pop()   # the local layer's own "end" mark: the next mark takes its place
+    else:
+        partial = local_layer(a1, a1s, w1_local, w2_local, wts, ids, mask, w1_scale_local, w2_scale_local)
+    _mark(timers, "ep_reduce_scatter")
     if world == 1:
         mine = partial
     else:
         mine = torch.empty((m_local, H), dtype=torch.float32, device=dev)
         dist.reduce_scatter_tensor(mine, partial, op=dist.ReduceOp.SUM, group=group)
-    return finalize(mine, dtype)
+    _mark(timers, "ep_finalize")
+    out = finalize(mine, dtype)
+    _mark(timers, "end")
+    return out

@@ -74,6 +74,14 @@ def moe_sorting(
         raise NotImplementedError("moe_sorting: flat=True (unsorted pass-through) is not supported")
     if output_aux:
         raise NotImplementedError("moe_sorting: output_aux=True is not supported")
+    return _moe_sorting_impl(topk_ids, topk_weights, num_experts, model_dim, moebuf_dtype, block_size,
+                             expert_mask, num_local_tokens, dispatch_policy, return_local_topk_ids,
+                             want_moe_buf=(expert_mask is not None) or accumulate)
+
+
+def _moe_sorting_impl(topk_ids, topk_weights, num_experts, model_dim, moebuf_dtype, block_size, expert_mask,
+                      num_local_tokens, dispatch_policy, return_local_topk_ids, want_moe_buf):
+    """aiter/fused_moe.py:175-288: allocates the outputs and calls the native sort."""
     if not topk_ids.is_cuda:
         raise RuntimeError("moe_sorting: topk_ids must be a CUDA tensor (there is no CPU path)")
     device = topk_ids.device
@@ -85,7 +93,7 @@ def moe_sorting(
     sorted_weights = torch.empty(max_num_tokens_padded, dtype=dtypes.fp32, device=device)
     sorted_expert_ids = torch.empty(max_num_m_blocks, dtype=dtypes.i32, device=device)
     num_valid_ids = torch.empty(2, dtype=dtypes.i32, device=device)
-    if (expert_mask is not None) or accumulate:
+    if want_moe_buf:
         moe_buf = torch.empty((M, model_dim), dtype=moebuf_dtype, device=device)
     else:
         moe_buf = torch.empty((0, 0), dtype=moebuf_dtype, device=device)
@@ -174,9 +182,10 @@ def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, 
     global_E = expert_mask.numel() if expert_mask is not None else E
 
     _mark(timers, "sort")
-    sorted_ids, sorted_weights, sorted_expert_ids, num_valid_ids, _ = moe_sorting(
-        topk_ids, topk_weight, global_E, model_dim, dtype, GEMM_BLOCK_M, expert_mask,
-        num_local_tokens, 0, accumulate=False)
+    # stage 2 accumulates into its own fp32 buffer, so no zero-filled moe_buf is asked for
+    sorted_ids, sorted_weights, sorted_expert_ids, num_valid_ids, _ = _moe_sorting_impl(
+        topk_ids, topk_weight, global_E, model_dim, dtypes.bf16, GEMM_BLOCK_M, expert_mask,
+        num_local_tokens, 0, False, want_moe_buf=False)
     _mark(timers, "quant")
     if hidden_states.dtype == dtypes.fp8:
         a1, a1_s = hidden_states.contiguous(), a1_scale.contiguous().view(M, -1)
@@ -195,6 +204,9 @@ def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, 
     _mark(timers, "stage2")
     _lib.call("b200_moe_stage2", a2, a2_s, w2, w2_scale, sorted_ids, sorted_weights, sorted_expert_ids,
               num_valid_ids, acc, status, device=device)
+    if dtype is None:        # caller wants the fp32 sums (expert parallelism reduces them across ranks first)
+        _mark(timers, "end")
+        return acc
     _mark(timers, "finalize")
     out = torch.empty((M, model_dim), dtype=dtype, device=device)
     _lib.call("b200_moe_finalize", out, acc, device=device)
