@@ -229,13 +229,18 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
         uint32_t it = 0;
         uint32_t tile_par = 0;
         bool ok = true;
+        int sid_next = 0;   // sorted id of this thread's row in the next tile, fetched one tile ahead
+        if (STAGE == 1 && (int)blockIdx.x < total_tiles)
+            sid_next = p.sorted_ids[((int)blockIdx.x / p.n_tiles) * BM + r];
         for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, tile_par ^= 1u) {
             const int blk = t / p.n_tiles, nt = t - blk * p.n_tiles;
             const int prow = blk * BM + r;
             uint32_t my_row;                 // source row of tile row r, or 0xFFFFFFFF for padding
             if (STAGE == 1) {
-                const int tok = p.sorted_ids[prow] & 0xFFFFFF;
+                const int tok = sid_next & 0xFFFFFF;
                 my_row = tok < tokens ? (uint32_t)tok : 0xFFFFFFFFu;
+                if (t + (int)gridDim.x < total_tiles)
+                    sid_next = p.sorted_ids[((t + (int)gridDim.x) / p.n_tiles) * BM + r];
             } else {
                 my_row = (uint32_t)prow;
             }
@@ -290,11 +295,27 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
         uint32_t it = 0;
         uint32_t tile_par = 0;
         bool ok = true;
+        // row info of the next tile is fetched one tile ahead, so its latency is off the path between
+        // two tiles (where the MMA warp can only run two K steps ahead of these warps)
+        int tok_next = 0;
+        float wgt_next = 0.f;
+        if ((int)blockIdx.x < total_tiles) {
+            const int prow0 = ((int)blockIdx.x / p.n_tiles) * BM + r;
+            tok_next = p.sorted_ids[prow0] & 0xFFFFFF;
+            if (STAGE == 2) wgt_next = p.sorted_w[prow0];
+        }
         for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, tile_par ^= 1u) {
             const int blk = t / p.n_tiles, nt = t - blk * p.n_tiles;
             const int prow = blk * BM + r;
-            const int tok = p.sorted_ids[prow] & 0xFFFFFF;
+            const int tok = tok_next;
             const bool valid = tok < tokens;
+            // stage 2: the route weight rides on the per-step scales (pads get 0)
+            const float wgt = (STAGE == 2) ? (valid ? wgt_next : 0.f) : 1.f;
+            if (t + (int)gridDim.x < total_tiles) {
+                const int prow1 = ((t + (int)gridDim.x) / p.n_tiles) * BM + r;
+                tok_next = p.sorted_ids[prow1] & 0xFFFFFF;
+                if (STAGE == 2) wgt_next = p.sorted_w[prow1];
+            }
             // a warp whose 32 rows are all padding (decode: most of them) leaves its accumulators at 0
             const bool warp_live = __any_sync(0xffffffffu, valid);
 
@@ -310,7 +331,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                 if (!(ok = ptx::mbar_wait<kEpilogueSleepNs>(tfull_bar(ts), tph, abort_flag))) break;
                 ptx::tc_fence_after();
                 const uint32_t slot = it % kScaleSlots;
-                const float sa = scale_a[slot * BM + r];
+                const float sa = (STAGE == 2) ? scale_a[slot * BM + r] * wgt : scale_a[slot * BM + r];
                 const float s0 = sa * scale_w[slot * 2], s1 = sa * scale_w[slot * 2 + 1];
                 const float2 s0v = make_float2(s0, s0), s1v = make_float2(s1, s1);
                 const uint32_t ta = lane_addr + ts * BN + half * 64;
@@ -380,12 +401,12 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                 for (int j = 0; j < 4; ++j) dst[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
                 if (half == 0) p.a2_scale[(size_t)prow * (p.inter / 128) + nt] = scale;
             } else {
-                // out[token] += weight * row  (aiter/fused_moe.py:3802-3811) as fp32 L2 reductions.
+                // out[token] += weight * row  (aiter/fused_moe.py:3802-3811) as fp32 L2 reductions; the
+                // weight is already in the accumulators (it rode on the per-step scales).
                 // A thread holds one row, so reductions issued straight from registers would hit 32
                 // different rows per instruction (16 B each).  Each warp instead passes 16-column
                 // chunks through a padded shared-memory buffer and re-reads them with 4 lanes per row:
                 // one instruction then covers 8 rows x 64 contiguous bytes.
-                const float wgt = valid ? p.sorted_w[prow] : 0.f;
                 const int my_tok = valid ? tok : -1;
                 const int H = p.n_rows;
                 float* sbuf = reinterpret_cast<float*>(smem + kOffStage) + (warp - kEpiWarp0) * (32 * kStageRow);
@@ -400,8 +421,8 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                             float4* wr = reinterpret_cast<float4*>(sbuf + lane * kStageRow);
 #pragma unroll
                             for (int j = 0; j < 4; ++j)
-                                wr[j] = make_float4(wgt * acc[a0 + 2 * j].x, wgt * acc[a0 + 2 * j].y,
-                                                    wgt * acc[a0 + 2 * j + 1].x, wgt * acc[a0 + 2 * j + 1].y);
+                                wr[j] = make_float4(acc[a0 + 2 * j].x, acc[a0 + 2 * j].y,
+                                                    acc[a0 + 2 * j + 1].x, acc[a0 + 2 * j + 1].y);
                             __syncwarp();
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {

@@ -256,10 +256,16 @@ __global__ void __launch_bounds__(kThreads, 1) sort_scan_kernel(SortArgs a) {
     int run = 0;
     const int e = threadIdx.x;
     if (e < a.E) {
-        for (int c = 0; c < a.nchunks; ++c) {
-            int v = a.ws_cnt[c * a.E + e];
-            a.ws_cnt[c * a.E + e] = run;  // routes of e in earlier chunks
-            run += v;
+        // 8 independent loads in flight at a time (the stores in between would otherwise serialise them)
+        for (int c0 = 0; c0 < a.nchunks; c0 += 8) {
+            int v[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) v[k] = (c0 + k < a.nchunks) ? __ldcg(a.ws_cnt + (c0 + k) * a.E + e) : 0;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                if (c0 + k < a.nchunks) a.ws_cnt[(c0 + k) * a.E + e] = run;  // routes of e in earlier chunks
+                run += v[k];
+            }
         }
     }
     layout_experts(a, run, local_id, base, warp_tot, tokens);

@@ -271,6 +271,7 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        os.environ["NCCL_DEBUG_FILE"] = "/dev/stderr"   # keep NCCL's banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=dev)
 
     def sync():
