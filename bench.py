@@ -146,8 +146,11 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    n_exp = 4
-    cb = cpu_baseline(n_exp=n_exp, steps=max(1, args.steps), warmup=min(args.warmup, 1))
+    n_exp = 32
+    # each step is a bounded sample (1/8 of the experts, all tokens); at most ~2 minutes of steps
+    probe = cpu_baseline(n_exp=n_exp, steps=1, warmup=0)
+    steps = max(1, min(args.steps, int(120.0 / max(probe["seconds_per_step"], 1e-3))))
+    cb = cpu_baseline(n_exp=n_exp, steps=steps, warmup=0) if steps > 1 else probe
     line = {
         "impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "TFLOP/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["seconds_per_step"] * 1e3,
@@ -155,7 +158,7 @@ def run_reference_arm(args):
         "data": "synthetic", "config": {"workload": WORKLOAD, "sample": cb["sample"]},
         "cpu_baseline": {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
+        "gpu_launches": 0, "steps_run": steps,
     }
     print(json.dumps(line))
 
@@ -376,7 +379,7 @@ def main():
                                        "peak_source": f"hbm_gbs of {pk['source']}"}}
         aiter_b200.check_device_status()
     if world == 1 and not args.no_cpu_baseline:
-        cb = cpu_baseline(n_exp=4)
+        cb = cpu_baseline(n_exp=64)
         line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
     if world > 1:
         line["gpu_launches"] = (3 + 4) * args.steps * 2
