@@ -27,7 +27,11 @@ void launch_moe_stage1(const aiter_tensor_t*, const aiter_tensor_t*, const aiter
                        aiter_tensor_t*, aiter_tensor_t*, cudaStream_t);
 void launch_moe_stage2(const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*,
                        const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*,
-                       aiter_tensor_t*, aiter_tensor_t*, cudaStream_t);
+                       aiter_tensor_t*, aiter_tensor_t*, int, int, int, cudaStream_t);
+
+void launch_biased_grouped_topk(const aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*, int, int,
+                                int, float, cudaStream_t);
+void launch_topk_softmax(aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*, const aiter_tensor_t*, int, cudaStream_t);
 
 namespace {
 
@@ -150,12 +154,35 @@ B200_EXPORT int b200_moe_stage1(const aiter_tensor_t* a1, const aiter_tensor_t* 
 B200_EXPORT int b200_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* a2_scale, const aiter_tensor_t* w2,
                     const aiter_tensor_t* w2_scale, const aiter_tensor_t* sorted_token_ids,
                     const aiter_tensor_t* sorted_weights, const aiter_tensor_t* sorted_expert_ids,
-                    const aiter_tensor_t* num_valid_ids, aiter_tensor_t* acc, aiter_tensor_t* status, void* stream) {
+                    const aiter_tensor_t* num_valid_ids, aiter_tensor_t* acc, aiter_tensor_t* status, int col_begin,
+                    int col_end, int sm_margin, void* stream) {
     return safe_call([&] {
         B200_CHECK(a2 != nullptr, "a2 must not be NULL");
         DeviceGuard g(a2->device_id);
         launch_moe_stage2(a2, a2_scale, w2, w2_scale, sorted_token_ids, sorted_weights, sorted_expert_ids,
-                          num_valid_ids, acc, status, (cudaStream_t)stream);
+                          num_valid_ids, acc, status, col_begin, col_end, sm_margin, (cudaStream_t)stream);
+    });
+}
+
+B200_EXPORT int b200_biased_grouped_topk(const aiter_tensor_t* gating_output, const aiter_tensor_t* correction_bias,
+                                         aiter_tensor_t* topk_weights, aiter_tensor_t* topk_ids, int num_expert_group,
+                                         int topk_group, int need_renorm, float routed_scaling_factor, void* stream) {
+    return safe_call([&] {
+        B200_CHECK(gating_output != nullptr, "gating_output must not be NULL");
+        DeviceGuard g(gating_output->device_id);
+        launch_biased_grouped_topk(gating_output, correction_bias, topk_weights, topk_ids, num_expert_group, topk_group,
+                                   need_renorm, routed_scaling_factor, (cudaStream_t)stream);
+    });
+}
+
+B200_EXPORT int b200_topk_softmax(aiter_tensor_t* topk_weights, aiter_tensor_t* topk_indices,
+                                  aiter_tensor_t* token_expert_indices, const aiter_tensor_t* gating_output,
+                                  int need_renorm, void* stream) {
+    return safe_call([&] {
+        B200_CHECK(gating_output != nullptr, "gating_output must not be NULL");
+        DeviceGuard g(gating_output->device_id);
+        launch_topk_softmax(topk_weights, topk_indices, token_expert_indices, gating_output, need_renorm,
+                            (cudaStream_t)stream);
     });
 }
 

@@ -78,7 +78,9 @@ struct GemmParams {
     const int* num_valid;    // {padded total, tokens}
     int M;                   // static token count
     int K, KB;               // K and K/128
-    int n_tiles;             // stage 1: I/128; stage 2: ceil(H/256)
+    int n_tiles;             // n-tiles this launch covers: stage 1 I/128; stage 2 ceil(columns/256)
+    int nt0;                 // first n-tile of this launch (stage 2 column range), else 0
+    int acc_ld;              // row pitch of acc in floats (stage 2)
     int n_rows;              // weight rows per expert: 2I (stage 1) or H (stage 2)
     int inter;               // I
     uint8_t* a2;             // stage 1 out [P, I] fp8
@@ -165,7 +167,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
         if (warp == 0 && lane == 0) {
             // ---------------------------------------------------------------- weight TMA producer
             auto tile_rows = [&](int t, int& r0, int& r1) {
-                const int blk = t / p.n_tiles, nt = t - blk * p.n_tiles;
+                const int blk = t / p.n_tiles, nt = t - blk * p.n_tiles + p.nt0;
                 const int e = p.sorted_eids[blk];
                 if (STAGE == 1) {
                     r0 = e * p.n_rows + nt * 128;   // gate rows
@@ -233,7 +235,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
         if (STAGE == 1 && (int)blockIdx.x < total_tiles)
             sid_next = p.sorted_ids[((int)blockIdx.x / p.n_tiles) * BM + r];
         for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, tile_par ^= 1u) {
-            const int blk = t / p.n_tiles, nt = t - blk * p.n_tiles;
+            const int blk = t / p.n_tiles, nt = t - blk * p.n_tiles + p.nt0;
             const int prow = blk * BM + r;
             uint32_t my_row;                 // source row of tile row r, or 0xFFFFFFFF for padding
             if (STAGE == 1) {
@@ -305,7 +307,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
             if (STAGE == 2) wgt_next = p.sorted_w[prow0];
         }
         for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, tile_par ^= 1u) {
-            const int blk = t / p.n_tiles, nt = t - blk * p.n_tiles;
+            const int blk = t / p.n_tiles, nt = t - blk * p.n_tiles + p.nt0;
             const int prow = blk * BM + r;
             const int tok = tok_next;
             const bool valid = tok < tokens;
@@ -429,7 +431,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                                 const int idx = i * 32 + lane, rr = idx >> 2, c4 = idx & 3;
                                 const float4 v = *reinterpret_cast<const float4*>(sbuf + rr * kStageRow + c4 * 4);
                                 const int tk = __shfl_sync(0xffffffffu, my_tok, rr);
-                                if (tk >= 0) ptx::red_add_v4(p.acc + (size_t)tk * H + col0 + c4 * 4, v.x, v.y, v.z, v.w);
+                                if (tk >= 0) ptx::red_add_v4(p.acc + (size_t)tk * p.acc_ld + (col0 - p.nt0 * 256) + c4 * 4, v.x, v.y, v.z, v.w);
                             }
                             __syncwarp();
                         }
@@ -490,14 +492,15 @@ CUtensorMap make_weight_map(const void* ptr, uint64_t rows, uint64_t K) {
 }
 
 template <int STAGE>
-void launch_gemm(const CUtensorMap& tmap, const GemmParams& p, int64_t max_tiles, int dev, cudaStream_t stream) {
+void launch_gemm(const CUtensorMap& tmap, const GemmParams& p, int64_t max_tiles, int dev, cudaStream_t stream,
+                 int sm_margin = 0) {
     static bool attr_set[64] = {false};
     if (dev >= 64 || !attr_set[dev]) {
         B200_CUDA(cudaFuncSetAttribute(moe_gemm_kernel<STAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        kSmemBytes));
         if (dev < 64) attr_set[dev] = true;
     }
-    int64_t grid = sm_count(dev);
+    int64_t grid = sm_count(dev) - sm_margin;   // SMs left free for a collective running beside this kernel
     if (max_tiles < grid) grid = max_tiles;
     if (grid < 1) return;
     moe_gemm_kernel<STAGE><<<(unsigned)grid, kThreads, kSmemBytes, stream>>>(tmap, p);
@@ -564,7 +567,7 @@ void launch_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* a2_scale,
                        const aiter_tensor_t* w2_scale, const aiter_tensor_t* sorted_ids,
                        const aiter_tensor_t* sorted_w, const aiter_tensor_t* sorted_eids,
                        const aiter_tensor_t* num_valid, aiter_tensor_t* acc, aiter_tensor_t* status,
-                       cudaStream_t stream) {
+                       int col_begin, int col_end, int sm_margin, cudaStream_t stream) {
     check_tensor(a2, "a2", AITER_DTYPE_fp8, 2);
     check_tensor(a2_scale, "a2_scale", AITER_DTYPE_fp32, -1);
     check_tensor(w2, "w2", AITER_DTYPE_fp8, 3);
@@ -579,7 +582,12 @@ void launch_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* a2_scale,
     const int64_t E = w2->shape[0], H = w2->shape[1];
     const int64_t M = acc->shape[0];
     B200_CHECK(w2->shape[2] == I, "w2 must be [E, model_dim, inter_dim]: K ", w2->shape[2], " != ", I);
-    B200_CHECK(acc->shape[1] == H, "acc must be [M, model_dim]");
+    if (col_end <= 0) col_end = (int)H;
+    B200_CHECK(col_begin >= 0 && col_begin < col_end && col_end <= H && col_begin % 256 == 0 &&
+                   (col_end % 256 == 0 || col_end == H),
+               "column range [", col_begin, ", ", col_end, ") must lie in [0, model_dim] on 256-column boundaries");
+    B200_CHECK(acc->shape[1] == col_end - col_begin, "acc must be [M, col_end - col_begin]");
+    B200_CHECK(sm_margin >= 0 && sm_margin < 128, "sm_margin must be in [0, 128)");
     B200_CHECK(I % 128 == 0 && H % 128 == 0, "inter_dim and model_dim must be multiples of 128");
     B200_CHECK((int64_t)a2_scale->numel_ >= P * (I / 128), "a2_scale must have P*inter_dim/128 elements");
     B200_CHECK((int64_t)w2_scale->numel_ == E * (H / 128) * (I / 128),
@@ -602,14 +610,16 @@ void launch_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* a2_scale,
     p.M = (int)M;
     p.K = (int)I;
     p.KB = (int)(I / 128);
-    p.n_tiles = (int)((H + 255) / 256);
+    p.n_tiles = (col_end - col_begin + 255) / 256;
+    p.nt0 = col_begin / 256;
+    p.acc_ld = col_end - col_begin;
     p.n_rows = (int)H;
     p.inter = (int)I;
     p.acc = (float*)acc->ptr;
     p.status = (int*)status->ptr;
     CUtensorMap tmap = make_weight_map(w2->ptr, (uint64_t)(E * H), (uint64_t)I);
     const int64_t max_tiles = ((int64_t)sorted_ids->numel_ / BM) * p.n_tiles;
-    launch_gemm<2>(tmap, p, max_tiles, a2->device_id, stream);
+    launch_gemm<2>(tmap, p, max_tiles, a2->device_id, stream, sm_margin);
 }
 
 }  // namespace b200

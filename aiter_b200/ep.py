@@ -37,10 +37,12 @@ def expert_mask_for_rank(num_experts: int, rank: int, world: int, device=None) -
     return mask
 
 
-def _gpu_local_layer(a1, a1_scale, w1, w2, topk_weight, topk_ids, expert_mask, w1_scale, w2_scale, timers=None):
-    """All rows, local experts -> fp32 partial [M, H] (no final rounding)."""
+def _gpu_local_layer(a1, a1_scale, w1, w2, topk_weight, topk_ids, expert_mask, w1_scale, w2_scale, timers=None,
+                     chunks=1, on_chunk=None, sm_margin=0):
+    """All rows, local experts -> fp32 partial [M, H] (or [chunks, M, H/chunks]); no final rounding."""
     return fused_moe_stages(a1, w1, w2, topk_weight, topk_ids, expert_mask, w1_scale, w2_scale,
-                            a1_scale, None, None, timers=timers)
+                            a1_scale, None, None, timers=timers, stage2_chunks=chunks, on_chunk=on_chunk,
+                            sm_margin=sm_margin)
 
 
 def _gpu_quant(x):
@@ -55,10 +57,13 @@ def _gpu_finalize(acc, dtype):
 
 def ep_fused_moe(x_local, w1_local, w2_local, topk_weight_local, topk_ids_local, w1_scale_local,
                  w2_scale_local, num_experts, group=None, dtype=torch.bfloat16,
-                 quant=_gpu_quant, local_layer=_gpu_local_layer, finalize=_gpu_finalize, timers=None):
+                 quant=_gpu_quant, local_layer=_gpu_local_layer, finalize=_gpu_finalize, timers=None,
+                 overlap_chunks=None, sm_margin=16):
     """x_local [M/G, H] bf16, routing [M/G, topk] with GLOBAL expert ids -> out [M/G, H].
 
-    Every rank must pass the same number of rows."""
+    Every rank must pass the same number of rows. With ``overlap_chunks`` > 1 (default: 4 on the GPU path
+    when H allows) stage 2 runs in that many column ranges and the reduce-scatter of a finished range
+    overlaps the computation of the next; ``sm_margin`` SMs are kept free for NCCL during those launches."""
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     m_local, H = x_local.shape
@@ -83,6 +88,31 @@ def ep_fused_moe(x_local, w1_local, w2_local, topk_weight_local, topk_ids_local,
         ids = side[:, kb:kb + topk].contiguous()
         wts = side[:, kb + topk:].contiguous().view(torch.float32)
     mask = expert_mask_for_rank(num_experts, rank, world, device=dev)
+    if overlap_chunks is None:
+        overlap_chunks = 4 if (world > 1 and local_layer is _gpu_local_layer and H % 1024 == 0) else 1
+    if overlap_chunks > 1:
+        # column ranges: the reduce-scatter of range c runs (on NCCL's stream) beside stage 2 of range c+1
+        hc = H // overlap_chunks
+        mine = torch.empty((overlap_chunks, m_local, hc), dtype=torch.float32, device=dev)
+        works = []
+
+        def on_chunk(c, block):
+            works.append(dist.reduce_scatter_tensor(mine[c], block, op=dist.ReduceOp.SUM, group=group,
+                                                    async_op=True))
+
+        partial = local_layer(a1, a1s, w1_local, w2_local, wts, ids, mask, w1_scale_local, w2_scale_local,
+                              timers=timers, chunks=overlap_chunks, on_chunk=on_chunk, sm_margin=sm_margin)
+        if timers is not None:
+            timers.pop()
+        _mark(timers, "ep_reduce_scatter")
+        for w in works:
+            w.wait()
+        _mark(timers, "ep_finalize")
+        out = finalize(mine.view(overlap_chunks * m_local, hc), dtype)
+        out = out.view(overlap_chunks, m_local, hc).permute(1, 0, 2).reshape(m_local, H)
+        _mark(timers, "end")
+        del partial
+        return out
     if timers is not None:
         partial = local_layer(a1, a1s, w1_local, w2_local, wts, ids, mask, w1_scale_local, w2_scale_local,
                               timers=timers)

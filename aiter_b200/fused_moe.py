@@ -169,9 +169,15 @@ def _mark(timers, name):
 
 
 def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, w1_scale, w2_scale,
-                     a1_scale, num_local_tokens, dtype, return_intermediates=False, timers=None):
+                     a1_scale, num_local_tokens, dtype, return_intermediates=False, timers=None,
+                     stage2_chunks=1, on_chunk=None, sm_margin=0):
     """sort -> a1 quant -> stage 1 -> stage 2 -> final rounding (the 2-stage flow of
     aiter/fused_moe.py:2979-3368 with the requant fused into stage 1).
+
+    ``stage2_chunks`` > 1 (with ``dtype=None``) computes the output columns in that many ranges, each into
+    its own contiguous fp32 block of the returned [chunks, M, H/chunks] tensor, calling
+    ``on_chunk(index, block)`` after each launch so the caller can start a collective on it while the
+    next range is computed; ``sm_margin`` SMs are left idle by those launches for the collective's kernels.
 
     ``timers``: optional list that receives (name, cuda event) marks recorded on the current
     stream before each kernel and at the end (the reference's per-stage bench hook,
@@ -200,10 +206,23 @@ def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, 
     _lib.call("b200_moe_stage1", a1, a1_s, w1, w1_scale, sorted_ids, sorted_expert_ids, num_valid_ids,
               a2, a2_s, status, device=device)
     _mark(timers, "zero")
+    if stage2_chunks > 1:
+        if dtype is not None or model_dim % (256 * stage2_chunks) != 0:
+            raise ValueError("stage2_chunks needs dtype=None and model_dim divisible by 256*chunks")
+        hc = model_dim // stage2_chunks
+        acc = torch.zeros((stage2_chunks, M, hc), dtype=dtypes.fp32, device=device)
+        _mark(timers, "stage2")
+        for c in range(stage2_chunks):
+            _lib.call("b200_moe_stage2", a2, a2_s, w2, w2_scale, sorted_ids, sorted_weights, sorted_expert_ids,
+                      num_valid_ids, acc[c], status, c * hc, (c + 1) * hc, int(sm_margin), device=device)
+            if on_chunk is not None:
+                on_chunk(c, acc[c])
+        _mark(timers, "end")
+        return acc
     acc = torch.zeros((M, model_dim), dtype=dtypes.fp32, device=device)
     _mark(timers, "stage2")
     _lib.call("b200_moe_stage2", a2, a2_s, w2, w2_scale, sorted_ids, sorted_weights, sorted_expert_ids,
-              num_valid_ids, acc, status, device=device)
+              num_valid_ids, acc, status, 0, 0, 0, device=device)
     if dtype is None:        # caller wants the fp32 sums (expert parallelism reduces them across ranks first)
         _mark(timers, "end")
         return acc

@@ -127,16 +127,38 @@ int b200_moe_stage1(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale,
  * per token in fp32.  Replaces ck_moe_stage2
  * (csrc/ck_gemm_moe_2stages_codegen/gemm_moe_ck2stages.cu:139-199).
  *   a2/a2_scale as written by stage 1; w2 [E,H,I] fp8 + w2_scale [E,H/128,I/128] fp32
- *   acc [M,H] fp32, must be zero on entry; receives sum over routes of weight * (a2 . w2) */
+ *   acc [M, col_end-col_begin] fp32, must be zero on entry; receives sum over routes of weight * (a2 . w2)
+ *   for the output columns [col_begin, col_end) (multiples of 256; col_end <= 0 means model_dim). Launching
+ *   the columns in several ranges lets a caller hand finished ranges to a collective while the next is computed;
+ *   sm_margin SMs are then left idle by this launch so that the collective's kernels can run beside it. */
 int b200_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* a2_scale,
                     const aiter_tensor_t* w2, const aiter_tensor_t* w2_scale,
                     const aiter_tensor_t* sorted_token_ids, const aiter_tensor_t* sorted_weights,
                     const aiter_tensor_t* sorted_expert_ids, const aiter_tensor_t* num_valid_ids,
-                    aiter_tensor_t* acc, aiter_tensor_t* status, void* stream);
+                    aiter_tensor_t* acc, aiter_tensor_t* status, int col_begin, int col_end, int sm_margin,
+                    void* stream);
 
 /* out[M,H] (bf16 or fp16) = round-to-nearest-even(acc[M,H] fp32): the single final rounding of
  * the reference's `out.sum(1).to(dtype)` (aiter/fused_moe.py:3811). */
 int b200_moe_finalize(aiter_tensor_t* out, const aiter_tensor_t* acc, void* stream);
+
+/* DeepSeek-V3 style router: sigmoid scores, correction bias for the choice only, groups ranked by the sum
+ * of their two best biased scores, top `topk_group` groups kept, top-k experts among them; weights are the
+ * un-biased scores, renormalised when asked, times routed_scaling_factor. Replaces biased_grouped_topk
+ * (aiter/ops/topk.py:89-99,176-215, csrc/kernels/topk_softmax_kernels_group.cu:1219-1266) with the arithmetic
+ * of biased_grouped_topk_torch (aiter/ops/topk.py:217-259).
+ *   gating_output [M,E] fp32|bf16, correction_bias [E] fp32|bf16 -> topk_weights [M,topk] fp32, topk_ids [M,topk] i32
+ *   E <= 1024, topk <= 32, num_expert_group <= 32 and a divisor of E */
+int b200_biased_grouped_topk(const aiter_tensor_t* gating_output, const aiter_tensor_t* correction_bias,
+                             aiter_tensor_t* topk_weights, aiter_tensor_t* topk_ids, int num_expert_group,
+                             int topk_group, int need_renorm, float routed_scaling_factor, void* stream);
+
+/* fp32 softmax over the experts, top-k, optional renormalisation. Replaces topk_softmax
+ * (aiter/ops/moe_op.py:29-66, csrc/kernels/topk_softmax_kernels.cu:769) as used by fused_topk
+ * (aiter/fused_moe.py:4058-4129). token_expert_indices is optional ([M,topk] i32 = k*M + token). */
+int b200_topk_softmax(aiter_tensor_t* topk_weights, aiter_tensor_t* topk_indices,
+                      aiter_tensor_t* token_expert_indices, const aiter_tensor_t* gating_output,
+                      int need_renorm, void* stream);
 
 #ifdef __cplusplus
 }

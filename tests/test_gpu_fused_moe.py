@@ -248,3 +248,21 @@ def test_cuda_graph_capture_and_replay():
                                    c["w2_scale"].cpu(), c2["topk_weight"].cpu(), c2["topk_ids"].cpu())
     assert_parity(out[:20], ref[:20], "graph replay")
     assert int((out[20:].view(torch.int16) != 0).sum()) == 0
+
+
+def test_stage2_column_ranges_equal_one_launch():
+    """Stage 2 launched in 4 column ranges (as the expert-parallel wrapper does to overlap its reduce-scatter)
+    leaves the same fp32 sums as one launch, up to the order of the fp32 reductions."""
+    c = to_dev(inputs.make_config("cfg0", seed=2))
+    args = (c["x"], c["w1_q"], c["w2_q"], c["topk_weight"], c["topk_ids"], None, c["w1_scale"], c["w2_scale"],
+            None, None, None)
+    whole = fm.fused_moe_stages(*args)
+    seen = []
+    parts = fm.fused_moe_stages(*args, stage2_chunks=4, on_chunk=lambda i, blk: seen.append((i, tuple(blk.shape))),
+                                sm_margin=16)
+    aiter_b200.check_device_status()
+    M, H = whole.shape
+    assert parts.shape == (4, M, H // 4) and seen == [(i, (M, H // 4)) for i in range(4)]
+    joined = parts.permute(1, 0, 2).reshape(M, H)
+    assert torch.allclose(joined, whole, rtol=1e-5, atol=1e-6)
+    assert float(whole.abs().max()) > 0
