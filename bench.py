@@ -160,7 +160,7 @@ def run_reference_arm(args):
         "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0, "steps_run": steps,
     }
-    print(json.dumps(line))
+    emit(line)
 
 
 # ------------------------------------------------------------------------------------------ GPU arm
@@ -239,6 +239,16 @@ def kernel_breakdown(fm, dev_args, reps=5):
     return {k: sum(v) / len(v) for k, v in acc.items()}
 
 
+def emit(line):
+    """The one JSON line goes to the real stdout; everything else this process (or a library such as NCCL,
+    which prints a version banner) writes to stdout has been pointed at stderr."""
+    os.write(_REAL_STDOUT, (json.dumps(line) + "\n").encode())
+
+
+_REAL_STDOUT = os.dup(1)
+os.dup2(2, 1)
+
+
 def main():
     global M_PREFILL, E, WORKLOAD
     ap = argparse.ArgumentParser()
@@ -274,7 +284,6 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        os.environ["NCCL_DEBUG_FILE"] = "/dev/stderr"   # keep NCCL's banner off stdout: one JSON line only
         dist.init_process_group("nccl", device_id=dev)
 
     def sync():
@@ -393,7 +402,7 @@ def main():
         line["ep_breakdown_ms_rank0"] = {k: round(sum(v) / len(v), 4) for k, v in accb.items()}
 
     if rank == 0:
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
