@@ -35,8 +35,12 @@ def _worker(rank, world, port, ret):
         sl = slice(rank * per, (rank + 1) * per)
         rows = slice(rank * m_local, (rank + 1) * m_local)
         d = lambda t: t.to(dev)
-        out = ep.ep_fused_moe(d(c["x"][rows]), d(c["w1_q"][sl]), d(c["w2_q"][sl]), d(c["topk_weight"][rows]),
-                              d(c["topk_ids"][rows]), d(c["w1_scale"][sl]), d(c["w2_scale"][sl]), E)
+        args = (d(c["x"][rows]), d(c["w1_q"][sl]), d(c["w2_q"][sl]), d(c["topk_weight"][rows]),
+                d(c["topk_ids"][rows]), d(c["w1_scale"][sl]), d(c["w2_scale"][sl]), E)
+        out = ep.ep_fused_moe(*args)
+        # the ranged variant (stage 2 in 4 column ranges, reduce-scatters issued beside it) agrees
+        out4 = ep.ep_fused_moe(*args, overlap_chunks=4)
+        assert float((out4.float() - out.float()).abs().max()) <= 0.04 * float(out.float().pow(2).mean().sqrt())
         torch.cuda.synchronize()
         aiter_b200.check_device_status()
         ret[rank] = out.cpu()
