@@ -13,6 +13,7 @@ from .fused_moe import (  # noqa: F401
     moe_sorting,
     moe_sorting_get_workspace_size,
     per_group_quant_hip,
+    per_token_quant_hip,
 )
 
 from .topk import biased_grouped_topk, fused_topk, topk_softmax  # noqa: F401,E402
@@ -20,5 +21,5 @@ from .topk import biased_grouped_topk, fused_topk, topk_softmax  # noqa: F401,E4
 __all__ = [
     "biased_grouped_topk", "fused_topk", "topk_softmax",
     "ActivationType", "QuantType", "dtypes", "fused_moe", "moe_sorting",
-    "moe_sorting_get_workspace_size", "get_hip_quant", "per_group_quant_hip", "check_device_status",
+    "moe_sorting_get_workspace_size", "get_hip_quant", "per_group_quant_hip", "per_token_quant_hip", "check_device_status",
 ]

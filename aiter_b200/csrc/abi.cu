@@ -22,12 +22,13 @@ void launch_moe_sorting_noalloc(const aiter_tensor_t*, const aiter_tensor_t*, ai
                                 aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*, int, int, const aiter_tensor_t*,
                                 const aiter_tensor_t*, aiter_tensor_t*, cudaStream_t);
 void launch_quant_1x128(aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*, cudaStream_t);
+void launch_quant_per_token(aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*, const aiter_tensor_t*, cudaStream_t);
 void launch_moe_stage1(const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*,
                        const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*,
-                       aiter_tensor_t*, aiter_tensor_t*, cudaStream_t);
+                       aiter_tensor_t*, aiter_tensor_t*, int, cudaStream_t);
 void launch_moe_stage2(const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*,
                        const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*,
-                       aiter_tensor_t*, aiter_tensor_t*, int, int, int, cudaStream_t);
+                       aiter_tensor_t*, aiter_tensor_t*, int, int, int, int, cudaStream_t);
 
 void launch_biased_grouped_topk(const aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*, int, int,
                                 int, float, cudaStream_t);
@@ -139,15 +140,24 @@ B200_EXPORT int b200_moe_quant_1x128(aiter_tensor_t* out, const aiter_tensor_t* 
     });
 }
 
+B200_EXPORT int b200_moe_quant_per_token(aiter_tensor_t* out, const aiter_tensor_t* input, aiter_tensor_t* scales,
+                                         const aiter_tensor_t* row_limit, void* stream) {
+    return safe_call([&] {
+        B200_CHECK(input != nullptr, "input must not be NULL");
+        DeviceGuard g(input->device_id);
+        launch_quant_per_token(out, input, scales, row_limit, (cudaStream_t)stream);
+    });
+}
+
 B200_EXPORT int b200_moe_stage1(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale, const aiter_tensor_t* w1,
                     const aiter_tensor_t* w1_scale, const aiter_tensor_t* sorted_token_ids,
                     const aiter_tensor_t* sorted_expert_ids, const aiter_tensor_t* num_valid_ids, aiter_tensor_t* a2,
-                    aiter_tensor_t* a2_scale, aiter_tensor_t* status, void* stream) {
+                    aiter_tensor_t* a2_scale, aiter_tensor_t* status, int quant_type, void* stream) {
     return safe_call([&] {
         B200_CHECK(a1 != nullptr, "a1 must not be NULL");
         DeviceGuard g(a1->device_id);
         launch_moe_stage1(a1, a1_scale, w1, w1_scale, sorted_token_ids, sorted_expert_ids, num_valid_ids, a2,
-                          a2_scale, status, (cudaStream_t)stream);
+                          a2_scale, status, quant_type, (cudaStream_t)stream);
     });
 }
 
@@ -155,12 +165,12 @@ B200_EXPORT int b200_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* 
                     const aiter_tensor_t* w2_scale, const aiter_tensor_t* sorted_token_ids,
                     const aiter_tensor_t* sorted_weights, const aiter_tensor_t* sorted_expert_ids,
                     const aiter_tensor_t* num_valid_ids, aiter_tensor_t* acc, aiter_tensor_t* status, int col_begin,
-                    int col_end, int sm_margin, void* stream) {
+                    int col_end, int sm_margin, int quant_type, void* stream) {
     return safe_call([&] {
         B200_CHECK(a2 != nullptr, "a2 must not be NULL");
         DeviceGuard g(a2->device_id);
         launch_moe_stage2(a2, a2_scale, w2, w2_scale, sorted_token_ids, sorted_weights, sorted_expert_ids,
-                          num_valid_ids, acc, status, col_begin, col_end, sm_margin, (cudaStream_t)stream);
+                          num_valid_ids, acc, status, col_begin, col_end, sm_margin, quant_type, (cudaStream_t)stream);
     });
 }
 

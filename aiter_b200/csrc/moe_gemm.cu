@@ -115,7 +115,11 @@ __device__ __forceinline__ void fold32(float2* acc, const uint32_t* v, float2 s)
         acc[j] = __ffma2_rn(make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1])), s, acc[j]);
 }
 
-template <int STAGE>
+// PT = false: 1x128 activation scales and 128x128 weight scales (QuantType.per_1x128 / per_128x128).
+// PT = true : one scale per activation row and one per weight output channel (QuantType.per_Token); the
+//             row scale rides on every K step, the channel scales are applied once in the epilogue, and
+//             stage 1 writes bf16 (the row-wise requantisation needs the whole row and is a kernel of its own).
+template <int STAGE, bool PT>
 __global__ void __launch_bounds__(kThreads, 1)
 moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -247,7 +251,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                 my_row = (uint32_t)prow;
             }
             const bool my_valid = my_row != 0xFFFFFFFFu;
-            const float* as_src = p.a_scale + (size_t)(my_valid ? my_row : 0u) * p.KB;
+            const float* as_src = p.a_scale + (size_t)(my_valid ? my_row : 0u) * (PT ? 1 : p.KB);
             row_tab[tile_par * BM + r] = my_row;
             ptx::named_barrier(2, BM);       // the 128 gather threads; table of the previous tile is
                                              // untouched (other parity), so one barrier per tile suffices
@@ -263,7 +267,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
             }
             // threads 0 and 1 also fetch the two weight-block scales of this tile
             const float* ws_src = p.w_scale;
-            if (r < 2) {
+            if (!PT && r < 2) {
                 const int e = p.sorted_eids[blk];
                 int nb;
                 if (STAGE == 1) nb = (r == 0) ? nt : p.inter / 128 + nt;
@@ -278,8 +282,8 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
 #pragma unroll
                 for (int i = 0; i < 8; ++i) ptx::cp_async16(dst + dst_off[i], src[i] + (size_t)kb * BK, nbytes[i]);
                 const uint32_t slot = it % kScaleSlots;
-                ptx::cp_async4(sbase + kOffScaleA + (slot * BM + r) * 4, as_src + kb, my_valid ? 4u : 0u);
-                if (r < 2) ptx::cp_async4(sbase + kOffScaleW + (slot * 2 + r) * 4, ws_src + kb, 4u);
+                ptx::cp_async4(sbase + kOffScaleA + (slot * BM + r) * 4, as_src + (PT ? 0 : kb), my_valid ? 4u : 0u);
+                if (!PT && r < 2) ptx::cp_async4(sbase + kOffScaleW + (slot * 2 + r) * 4, ws_src + kb, 4u);
                 // the arrival is delivered by the copy engine when this thread's copies have landed,
                 // so the thread can go on to the next stage at once (all kStages stay in flight)
                 ptx::cp_async_mbar_arrive(full_bar(s));
@@ -334,7 +338,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                 ptx::tc_fence_after();
                 const uint32_t slot = it % kScaleSlots;
                 const float sa = (STAGE == 2) ? scale_a[slot * BM + r] * wgt : scale_a[slot * BM + r];
-                const float s0 = sa * scale_w[slot * 2], s1 = sa * scale_w[slot * 2 + 1];
+                const float s0 = PT ? sa : sa * scale_w[slot * 2], s1 = PT ? sa : sa * scale_w[slot * 2 + 1];
                 const float2 s0v = make_float2(s0, s0), s1v = make_float2(s1, s1);
                 const uint32_t ta = lane_addr + ts * BN + half * 64;
                 // Four 32-column chunks: load + wait, then 16 packed FMAs.  The packed fp32x2 FMAs matter:
@@ -359,7 +363,36 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
             }
             if (!ok) break;
 
-            if (STAGE == 1) {
+            if (PT) {
+                // weight scales per output channel: column j of the first group is weight row
+                // e*n_rows + c0 + j, of the second group c1 + j (all lanes read the same addresses)
+                const int e = p.sorted_eids[blk];
+                const int c0 = (STAGE == 1) ? nt * 128 + half * 64 : nt * 256 + half * 64;
+                const int c1 = (STAGE == 1) ? p.inter + c0 : min(c0 + 128, p.n_rows - 64);
+                const float4* w0 = reinterpret_cast<const float4*>(p.w_scale + (size_t)e * p.n_rows + c0);
+                const float4* w1 = reinterpret_cast<const float4*>(p.w_scale + (size_t)e * p.n_rows + c1);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const float4 a = __ldg(w0 + j), b = __ldg(w1 + j);
+                    acc[2 * j] = make_float2(acc[2 * j].x * a.x, acc[2 * j].y * a.y);
+                    acc[2 * j + 1] = make_float2(acc[2 * j + 1].x * a.z, acc[2 * j + 1].y * a.w);
+                    acc[32 + 2 * j] = make_float2(acc[32 + 2 * j].x * b.x, acc[32 + 2 * j].y * b.y);
+                    acc[32 + 2 * j + 1] = make_float2(acc[32 + 2 * j + 1].x * b.z, acc[32 + 2 * j + 1].y * b.w);
+                }
+            }
+
+            if (STAGE == 1 && PT) {
+                // SiLU(gate)*up -> bf16, written in sorted-row order; the row-wise quantisation follows
+                uint32_t w[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(silu_mul(acc[j].x, acc[32 + j].x), silu_mul(acc[j].y, acc[32 + j].y));
+                    w[j] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                uint4* dst = reinterpret_cast<uint4*>(p.a2 + ((size_t)prow * p.inter + nt * 128 + half * 64) * 2);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) dst[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+            } else if (STAGE == 1) {
                 // SiLU(gate)*up in fp32 -> bf16 (RNE) -> 1x128 requant, as the oracle does:
                 // aiter/fused_moe.py:3668-3681 then aiter/ops/quant.py:64-94 on the bf16 values.
                 float amax = 0.f;
@@ -491,19 +524,19 @@ CUtensorMap make_weight_map(const void* ptr, uint64_t rows, uint64_t K) {
     return m;
 }
 
-template <int STAGE>
+template <int STAGE, bool PT>
 void launch_gemm(const CUtensorMap& tmap, const GemmParams& p, int64_t max_tiles, int dev, cudaStream_t stream,
                  int sm_margin = 0) {
     static bool attr_set[64] = {false};
     if (dev >= 64 || !attr_set[dev]) {
-        B200_CUDA(cudaFuncSetAttribute(moe_gemm_kernel<STAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        B200_CUDA(cudaFuncSetAttribute(moe_gemm_kernel<STAGE, PT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        kSmemBytes));
         if (dev < 64) attr_set[dev] = true;
     }
     int64_t grid = sm_count(dev) - sm_margin;   // SMs left free for a collective running beside this kernel
     if (max_tiles < grid) grid = max_tiles;
     if (grid < 1) return;
-    moe_gemm_kernel<STAGE><<<(unsigned)grid, kThreads, kSmemBytes, stream>>>(tmap, p);
+    moe_gemm_kernel<STAGE, PT><<<(unsigned)grid, kThreads, kSmemBytes, stream>>>(tmap, p);
     B200_CUDA(cudaGetLastError());
 }
 
@@ -512,7 +545,11 @@ void launch_gemm(const CUtensorMap& tmap, const GemmParams& p, int64_t max_tiles
 void launch_moe_stage1(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale, const aiter_tensor_t* w1,
                        const aiter_tensor_t* w1_scale, const aiter_tensor_t* sorted_ids,
                        const aiter_tensor_t* sorted_eids, const aiter_tensor_t* num_valid, aiter_tensor_t* a2,
-                       aiter_tensor_t* a2_scale, aiter_tensor_t* status, cudaStream_t stream) {
+                       aiter_tensor_t* a2_scale, aiter_tensor_t* status, int quant_type, cudaStream_t stream) {
+    // quant_type: QuantType of the reference (csrc/include/aiter_enum.h:16-26): 4/5 = block scale, 2 = per_Token
+    B200_CHECK(quant_type == 4 || quant_type == 5 || quant_type == 2,
+               "quant_type must be per_1x128 (4), per_128x128 (5) or per_Token (2), got ", quant_type);
+    const bool pt = quant_type == 2;
     check_tensor(a1, "a1", AITER_DTYPE_fp8, 2);
     check_tensor(a1_scale, "a1_scale", AITER_DTYPE_fp32, -1);
     check_tensor(w1, "w1", AITER_DTYPE_fp8, 3);
@@ -520,8 +557,8 @@ void launch_moe_stage1(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale,
     check_tensor(sorted_ids, "sorted_token_ids", AITER_DTYPE_i32, 1);
     check_tensor(sorted_eids, "sorted_expert_ids", AITER_DTYPE_i32, 1);
     check_tensor(num_valid, "num_valid_ids", AITER_DTYPE_i32, 1);
-    check_tensor(a2, "a2", AITER_DTYPE_fp8, 2);
-    check_tensor(a2_scale, "a2_scale", AITER_DTYPE_fp32, -1);
+    check_tensor(a2, "a2", pt ? AITER_DTYPE_bf16 : AITER_DTYPE_fp8, 2);
+    if (!pt) check_tensor(a2_scale, "a2_scale", AITER_DTYPE_fp32, -1);
     check_tensor(status, "status", AITER_DTYPE_i32, -1);
     const int64_t M = a1->shape[0], H = a1->shape[1];
     const int64_t E = w1->shape[0], N2 = w1->shape[1];
@@ -529,18 +566,24 @@ void launch_moe_stage1(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale,
     B200_CHECK(N2 % 256 == 0, "2*inter_dim must be a multiple of 256 (inter_dim % 128 == 0), got ", N2);
     B200_CHECK(H % 128 == 0, "model_dim must be a multiple of 128, got ", H);
     const int64_t I = N2 / 2;
-    B200_CHECK((int64_t)a1_scale->numel_ == M * (H / 128), "a1_scale must have M*model_dim/128 elements");
-    B200_CHECK((int64_t)w1_scale->numel_ == E * (N2 / 128) * (H / 128),
-               "w1_scale must have E*(2*inter_dim/128)*(model_dim/128) elements");
+    if (pt) {
+        B200_CHECK((int64_t)a1_scale->numel_ == M, "a1_scale must have one element per token for per_Token");
+        B200_CHECK((int64_t)w1_scale->numel_ == E * N2, "w1_scale must have E*2*inter_dim elements for per_Token");
+    } else {
+        B200_CHECK((int64_t)a1_scale->numel_ == M * (H / 128), "a1_scale must have M*model_dim/128 elements");
+        B200_CHECK((int64_t)w1_scale->numel_ == E * (N2 / 128) * (H / 128),
+                   "w1_scale must have E*(2*inter_dim/128)*(model_dim/128) elements");
+    }
     const int64_t P = a2->shape[0];
     B200_CHECK(a2->shape[1] == I, "a2 must be [P, inter_dim]");
     B200_CHECK((int64_t)sorted_ids->numel_ >= 1 && P >= (int64_t)sorted_ids->numel_,
                "a2 must have at least as many rows as sorted_token_ids (", sorted_ids->numel_, "), has ", P);
-    B200_CHECK((int64_t)a2_scale->numel_ >= P * (I / 128), "a2_scale must have P*inter_dim/128 elements");
+    if (!pt) B200_CHECK((int64_t)a2_scale->numel_ >= P * (I / 128), "a2_scale must have P*inter_dim/128 elements");
     B200_CHECK(num_valid->numel_ >= 2 && status->numel_ >= 1, "num_valid_ids needs 2 and status 1 element");
     B200_CHECK(E * N2 < ((int64_t)1 << 31) && M < (1 << 24), "problem too large");
-    B200_CHECK(((uintptr_t)a1->ptr & 15) == 0 && ((uintptr_t)w1->ptr & 15) == 0 && ((uintptr_t)a2->ptr & 15) == 0,
-               "a1, w1 and a2 must be 16-byte aligned");
+    B200_CHECK(((uintptr_t)a1->ptr & 15) == 0 && ((uintptr_t)w1->ptr & 15) == 0 && ((uintptr_t)a2->ptr & 15) == 0 &&
+                   ((uintptr_t)w1_scale->ptr & 15) == 0,
+               "a1, w1, w1_scale and a2 must be 16-byte aligned");
 
     GemmParams p{};
     p.a = (const uint8_t*)a1->ptr;
@@ -556,18 +599,22 @@ void launch_moe_stage1(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale,
     p.n_rows = (int)N2;
     p.inter = (int)I;
     p.a2 = (uint8_t*)a2->ptr;
-    p.a2_scale = (float*)a2_scale->ptr;
+    p.a2_scale = pt ? nullptr : (float*)a2_scale->ptr;
     p.status = (int*)status->ptr;
     CUtensorMap tmap = make_weight_map(w1->ptr, (uint64_t)(E * N2), (uint64_t)H);
     const int64_t max_tiles = ((int64_t)sorted_ids->numel_ / BM) * p.n_tiles;
-    launch_gemm<1>(tmap, p, max_tiles, a1->device_id, stream);
+    if (pt) launch_gemm<1, true>(tmap, p, max_tiles, a1->device_id, stream);
+    else launch_gemm<1, false>(tmap, p, max_tiles, a1->device_id, stream);
 }
 
 void launch_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* a2_scale, const aiter_tensor_t* w2,
                        const aiter_tensor_t* w2_scale, const aiter_tensor_t* sorted_ids,
                        const aiter_tensor_t* sorted_w, const aiter_tensor_t* sorted_eids,
                        const aiter_tensor_t* num_valid, aiter_tensor_t* acc, aiter_tensor_t* status,
-                       int col_begin, int col_end, int sm_margin, cudaStream_t stream) {
+                       int col_begin, int col_end, int sm_margin, int quant_type, cudaStream_t stream) {
+    B200_CHECK(quant_type == 4 || quant_type == 5 || quant_type == 2,
+               "quant_type must be per_1x128 (4), per_128x128 (5) or per_Token (2), got ", quant_type);
+    const bool pt = quant_type == 2;
     check_tensor(a2, "a2", AITER_DTYPE_fp8, 2);
     check_tensor(a2_scale, "a2_scale", AITER_DTYPE_fp32, -1);
     check_tensor(w2, "w2", AITER_DTYPE_fp8, 3);
@@ -589,9 +636,15 @@ void launch_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* a2_scale,
     B200_CHECK(acc->shape[1] == col_end - col_begin, "acc must be [M, col_end - col_begin]");
     B200_CHECK(sm_margin >= 0 && sm_margin < 128, "sm_margin must be in [0, 128)");
     B200_CHECK(I % 128 == 0 && H % 128 == 0, "inter_dim and model_dim must be multiples of 128");
-    B200_CHECK((int64_t)a2_scale->numel_ >= P * (I / 128), "a2_scale must have P*inter_dim/128 elements");
-    B200_CHECK((int64_t)w2_scale->numel_ == E * (H / 128) * (I / 128),
-               "w2_scale must have E*(model_dim/128)*(inter_dim/128) elements");
+    if (pt) {
+        B200_CHECK((int64_t)a2_scale->numel_ >= P, "a2_scale must have one element per sorted row for per_Token");
+        B200_CHECK((int64_t)w2_scale->numel_ == E * H, "w2_scale must have E*model_dim elements for per_Token");
+        B200_CHECK(((uintptr_t)w2_scale->ptr & 15) == 0, "w2_scale must be 16-byte aligned");
+    } else {
+        B200_CHECK((int64_t)a2_scale->numel_ >= P * (I / 128), "a2_scale must have P*inter_dim/128 elements");
+        B200_CHECK((int64_t)w2_scale->numel_ == E * (H / 128) * (I / 128),
+                   "w2_scale must have E*(model_dim/128)*(inter_dim/128) elements");
+    }
     B200_CHECK(P >= (int64_t)sorted_ids->numel_ && sorted_w->numel_ >= sorted_ids->numel_,
                "a2 and sorted_weights must cover sorted_token_ids");
     B200_CHECK(num_valid->numel_ >= 2 && status->numel_ >= 1, "num_valid_ids needs 2 and status 1 element");
@@ -619,7 +672,8 @@ void launch_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* a2_scale,
     p.status = (int*)status->ptr;
     CUtensorMap tmap = make_weight_map(w2->ptr, (uint64_t)(E * H), (uint64_t)I);
     const int64_t max_tiles = ((int64_t)sorted_ids->numel_ / BM) * p.n_tiles;
-    launch_gemm<2>(tmap, p, max_tiles, a2->device_id, stream, sm_margin);
+    if (pt) launch_gemm<2, true>(tmap, p, max_tiles, a2->device_id, stream, sm_margin);
+    else launch_gemm<2, false>(tmap, p, max_tiles, a2->device_id, stream, sm_margin);
 }
 
 }  // namespace b200

@@ -54,7 +54,81 @@ __global__ void __launch_bounds__(kQuantThreads) quant_1x128_kernel(
     }
 }
 
+// Per-row dynamic FP8 quantisation over the whole row (QuantType.per_Token): one CTA per row, the row is
+// kept in shared memory between the amax pass and the conversion pass. Same rounding sequence as above
+// (aiter/ops/quant.py:64-94 over the last dimension). Rows >= *row_limit (if given) are skipped.
+__global__ void __launch_bounds__(256) quant_per_token_kernel(const uint4* __restrict__ x, uint2* __restrict__ q,
+                                                              float* __restrict__ scales, int cols8,
+                                                              const int* __restrict__ row_limit) {
+    extern __shared__ uint4 row_s[];
+    __shared__ float red[8];
+    const int64_t row = blockIdx.x;
+    if (row_limit && row >= *row_limit) return;
+    float amax = 0.f;
+    for (int i = threadIdx.x; i < cols8; i += blockDim.x) {
+        const uint4 raw = __ldg(x + row * cols8 + i);
+        row_s[i] = raw;
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 f = __bfloat1622float2(h[k]);
+            amax = fmaxf(amax, fmaxf(fabsf(f.x), fabsf(f.y)));
+        }
+    }
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = amax;
+    __syncthreads();
+    amax = red[0];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) amax = fmaxf(amax, red[k]);
+    float scale = __fdiv_rn(amax, 448.0f);
+    if (scale == 0.f) scale = 1.f;
+    for (int i = threadIdx.x; i < cols8; i += blockDim.x) {
+        const uint4 raw = row_s[i];
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        uint32_t w[2];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const float2 a = __bfloat1622float2(h[2 * k]), b = __bfloat1622float2(h[2 * k + 1]);
+            const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(a.x, scale), __fdiv_rn(a.y, scale)),
+                                                         __NV_SATFINITE, __NV_E4M3);
+            const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(b.x, scale), __fdiv_rn(b.y, scale)),
+                                                         __NV_SATFINITE, __NV_E4M3);
+            w[k] = lo | (hi << 16);
+        }
+        q[row * cols8 + i] = make_uint2(w[0], w[1]);
+    }
+    if (threadIdx.x == 0) scales[row] = scale;
+}
+
 }  // namespace
+
+void launch_quant_per_token(aiter_tensor_t* out, const aiter_tensor_t* input, aiter_tensor_t* scales,
+                            const aiter_tensor_t* row_limit, cudaStream_t stream) {
+    check_tensor(input, "input", AITER_DTYPE_bf16, 2);
+    check_tensor(out, "out", AITER_DTYPE_fp8, 2);
+    check_tensor(scales, "scales", AITER_DTYPE_fp32, -1);
+    const int64_t rows = input->shape[0], cols = input->shape[1];
+    B200_CHECK(cols % 8 == 0 && cols >= 8, "row length must be a multiple of 8, got ", cols);
+    B200_CHECK(cols * 2 <= 200 * 1024, "row too long for the shared-memory row cache: ", cols);
+    B200_CHECK(out->shape[0] == rows && out->shape[1] == cols, "out must have the shape of input");
+    B200_CHECK((int64_t)scales->numel_ >= rows, "scales needs one element per row");
+    B200_CHECK(((uintptr_t)input->ptr & 15) == 0 && ((uintptr_t)out->ptr & 7) == 0, "input must be 16-byte and out 8-byte aligned");
+    if (row_limit) check_tensor(row_limit, "row_limit", AITER_DTYPE_i32, -1);
+    if (rows == 0) return;
+    const size_t smem = (size_t)cols * 2;
+    static bool attr_set[64] = {false};
+    const int dev = input->device_id;
+    if (dev >= 64 || !attr_set[dev]) {
+        B200_CUDA(cudaFuncSetAttribute(quant_per_token_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        if (dev < 64) attr_set[dev] = true;
+    }
+    quant_per_token_kernel<<<(unsigned)rows, 256, smem, stream>>>((const uint4*)input->ptr, (uint2*)out->ptr,
+                                                                   (float*)scales->ptr, (int)(cols / 8),
+                                                                   row_limit ? (const int*)row_limit->ptr : nullptr);
+    B200_CUDA(cudaGetLastError());
+}
 
 void launch_quant_1x128(aiter_tensor_t* out, const aiter_tensor_t* input, aiter_tensor_t* scales,
                         cudaStream_t stream) {

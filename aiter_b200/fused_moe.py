@@ -137,11 +137,32 @@ def per_group_quant_hip(x, scale=None, quant_dtype=dtypes.fp8, group_size=128, t
     return y, y_scale
 
 
+def per_token_quant_hip(x, scale=None, quant_dtype=dtypes.fp8, row_limit=None):
+    """Per-row dynamic FP8 quantisation, signature of aiter/ops/quant.py:406-436.
+    x [..., C] bf16 -> (codes [..., C] e4m3, scales [..., 1] fp32). ``row_limit``: optional device int32
+    [1]; rows at or past it are left untouched."""
+    if scale is not None:
+        raise NotImplementedError("per_token_quant_hip: static scale is not supported")
+    if quant_dtype != dtypes.fp8:
+        raise NotImplementedError("per_token_quant_hip: only quant_dtype=fp8 (e4m3fn) is supported")
+    if x.dtype != dtypes.bf16:
+        raise NotImplementedError(f"per_token_quant_hip: input must be bf16, got {x.dtype}")
+    x = x.contiguous()
+    cols = x.shape[-1]
+    x2 = x.view(-1, cols)
+    y = torch.empty(x2.shape, dtype=dtypes.fp8, device=x.device)
+    y_scale = torch.empty((x2.shape[0],), dtype=dtypes.fp32, device=x.device)
+    _lib.call("b200_moe_quant_per_token", y, x2, y_scale, row_limit, device=x.device)
+    return y.view(x.shape), y_scale.view(*x.shape[:-1], 1)
+
+
 def get_hip_quant(qType):
-    """aiter/ops/quant.py:367-387, restricted to the block-scale path."""
+    """aiter/ops/quant.py:367-387, restricted to the FP8 paths built here."""
     qType = quant_remap.get(QuantType(qType), QuantType(qType))
+    if qType == QuantType.per_Token:
+        return per_token_quant_hip
     if qType != QuantType.per_1x128:
-        raise NotImplementedError(f"get_hip_quant: only per_1x128 / per_128x128 are supported, got {qType!r}")
+        raise NotImplementedError(f"get_hip_quant: only per_1x128 / per_128x128 / per_Token are supported, got {qType!r}")
     return per_group_quant_hip
 
 
@@ -170,7 +191,7 @@ def _mark(timers, name):
 
 def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, w1_scale, w2_scale,
                      a1_scale, num_local_tokens, dtype, return_intermediates=False, timers=None,
-                     stage2_chunks=1, on_chunk=None, sm_margin=0):
+                     stage2_chunks=1, on_chunk=None, sm_margin=0, quant_type=QuantType.per_1x128):
     """sort -> a1 quant -> stage 1 -> stage 2 -> final rounding (the 2-stage flow of
     aiter/fused_moe.py:2979-3368 with the requant fused into stage 1).
 
@@ -193,18 +214,33 @@ def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, 
         topk_ids, topk_weight, global_E, model_dim, dtypes.bf16, GEMM_BLOCK_M, expert_mask,
         num_local_tokens, 0, False, want_moe_buf=False)
     _mark(timers, "quant")
+    per_token = QuantType(quant_type) == QuantType.per_Token
+    qt = int(QuantType.per_Token if per_token else QuantType.per_1x128)
     if hidden_states.dtype == dtypes.fp8:
         a1, a1_s = hidden_states.contiguous(), a1_scale.contiguous().view(M, -1)
+    elif per_token:
+        a1, a1_s = per_token_quant_hip(hidden_states)
     else:
         a1, a1_s = per_group_quant_hip(hidden_states)
 
     P = sorted_ids.numel()
-    a2 = torch.empty((P, inter_dim), dtype=dtypes.fp8, device=device)
-    a2_s = torch.empty((P, inter_dim // 128), dtype=dtypes.fp32, device=device)
     status = _status(device)
     _mark(timers, "stage1")
-    _lib.call("b200_moe_stage1", a1, a1_s, w1, w1_scale, sorted_ids, sorted_expert_ids, num_valid_ids,
-              a2, a2_s, status, device=device)
+    if per_token:
+        # stage 1 leaves the bf16 activation in sorted-row order; the row scale needs the whole row,
+        # so the requantisation is a pass of its own over the valid rows (num_valid_ids[0] on the device)
+        a2_bf16 = torch.empty((P, inter_dim), dtype=dtypes.bf16, device=device)
+        _lib.call("b200_moe_stage1", a1, a1_s, w1, w1_scale, sorted_ids, sorted_expert_ids, num_valid_ids,
+                  a2_bf16, None, status, qt, device=device)
+        _mark(timers, "requant")
+        a2 = torch.empty((P, inter_dim), dtype=dtypes.fp8, device=device)
+        a2_s = torch.empty((P,), dtype=dtypes.fp32, device=device)
+        _lib.call("b200_moe_quant_per_token", a2, a2_bf16, a2_s, num_valid_ids, device=device)
+    else:
+        a2 = torch.empty((P, inter_dim), dtype=dtypes.fp8, device=device)
+        a2_s = torch.empty((P, inter_dim // 128), dtype=dtypes.fp32, device=device)
+        _lib.call("b200_moe_stage1", a1, a1_s, w1, w1_scale, sorted_ids, sorted_expert_ids, num_valid_ids,
+                  a2, a2_s, status, qt, device=device)
     _mark(timers, "zero")
     if stage2_chunks > 1:
         if dtype is not None or model_dim % (256 * stage2_chunks) != 0:
@@ -214,7 +250,7 @@ def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, 
         _mark(timers, "stage2")
         for c in range(stage2_chunks):
             _lib.call("b200_moe_stage2", a2, a2_s, w2, w2_scale, sorted_ids, sorted_weights, sorted_expert_ids,
-                      num_valid_ids, acc[c], status, c * hc, (c + 1) * hc, int(sm_margin), device=device)
+                      num_valid_ids, acc[c], status, c * hc, (c + 1) * hc, int(sm_margin), qt, device=device)
             if on_chunk is not None:
                 on_chunk(c, acc[c])
         _mark(timers, "end")
@@ -222,7 +258,7 @@ def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, 
     acc = torch.zeros((M, model_dim), dtype=dtypes.fp32, device=device)
     _mark(timers, "stage2")
     _lib.call("b200_moe_stage2", a2, a2_s, w2, w2_scale, sorted_ids, sorted_weights, sorted_expert_ids,
-              num_valid_ids, acc, status, 0, 0, 0, device=device)
+              num_valid_ids, acc, status, 0, 0, 0, qt, device=device)
     if dtype is None:        # caller wants the fp32 sums (expert parallelism reduces them across ranks first)
         _mark(timers, "end")
         return acc
@@ -284,10 +320,10 @@ def fused_moe(
     ``block_size_M`` is accepted and ignored: the GEMM row tile is fixed at 128, which only
     changes how the routes are padded, not the result."""
     quant_type = quant_remap.get(QuantType(quant_type), QuantType(quant_type))
-    if quant_type != QuantType.per_1x128:
+    if quant_type not in (QuantType.per_1x128, QuantType.per_Token):
         raise NotImplementedError(
             f"fused_moe: quant_type={QuantType(quant_type)!r} is not supported; this build covers "
-            "QuantType.per_1x128 / per_128x128 (FP8 block scale)")
+            "QuantType.per_1x128 / per_128x128 (FP8 block scale) and QuantType.per_Token (FP8)")
     if ActivationType(activation) != ActivationType.Silu:
         raise NotImplementedError(f"fused_moe: activation={ActivationType(activation)!r} is not supported (Silu only)")
     _check_unsupported(
@@ -305,7 +341,7 @@ def fused_moe(
     if w1.dtype != dtypes.fp8 or w2.dtype != dtypes.fp8:
         raise NotImplementedError(f"fused_moe: weights must be float8_e4m3fn, got {w1.dtype}/{w2.dtype}")
     if w1_scale is None or w2_scale is None:
-        raise ValueError("fused_moe: w1_scale and w2_scale are required for block-scale quantisation")
+        raise ValueError("fused_moe: w1_scale and w2_scale are required for FP8 quantisation")
     M, topk = topk_ids.shape
     E, model_dim, inter_dim = get_inter_dim(w1.shape, w2.shape)
     if w1.shape[1] != 2 * inter_dim:
@@ -317,7 +353,7 @@ def fused_moe(
         raise ValueError(f"fused_moe: hidden_states must be [{M}, {model_dim}], got {tuple(hidden_states.shape)}")
     if hidden_states.dtype == dtypes.fp8:
         if a1_scale is None:
-            raise ValueError("fused_moe: fp8 hidden_states need a1_scale [M, model_dim/128]")
+            raise ValueError("fused_moe: fp8 hidden_states need a1_scale ([M, model_dim/128], or [M, 1] for per_Token)")
         dtype = dtypes.bf16 if dtype is None else dtype
     else:
         if hidden_states.dtype != dtypes.bf16:
@@ -333,4 +369,4 @@ def fused_moe(
         raise ValueError("fused_moe: topk_ids must be int32")
     return fused_moe_stages(hidden_states, w1.contiguous(), w2.contiguous(), topk_weight, topk_ids,
                             expert_mask, w1_scale.contiguous(), w2_scale.contiguous(), a1_scale,
-                            num_local_tokens, dtype)
+                            num_local_tokens, dtype, quant_type=quant_type)

@@ -108,6 +108,15 @@ int b200_moe_sorting_fwd_noalloc(const aiter_tensor_t* topk_ids, const aiter_ten
 int b200_moe_quant_1x128(aiter_tensor_t* out, const aiter_tensor_t* input, aiter_tensor_t* scales,
                          void* stream);
 
+/* Dynamic per-row FP8 e4m3 quantisation over the whole row (QuantType.per_Token): scale = amax/448
+ * (1 when amax is 0), codes = RNE(x / scale). Replaces dynamic_per_token_scaled_quant
+ * (aiter/ops/quant.py:406-436, csrc/kernels/quant_kernels.cu) with the rounding sequence of pertoken_quant
+ * (aiter/ops/quant.py:64-94).
+ *   input [R,C] bf16 -> out [R,C] fp8, scales [R] fp32; row_limit: optional [1] i32 on the device, rows >= it
+ *   are skipped (the padded tail of a sorted buffer) */
+int b200_moe_quant_per_token(aiter_tensor_t* out, const aiter_tensor_t* input, aiter_tensor_t* scales,
+                             const aiter_tensor_t* row_limit, void* stream);
+
 /* Stage 1: grouped gate/up GEMM over the sorted blocks + SiLU(gate)*up + bf16 rounding +
  * 1x128 FP8 requantisation.  Replaces ck_moe_stage1 followed by the a2 quant
  * (csrc/ck_gemm_moe_2stages_codegen/gemm_moe_ck2stages.cu:68-137, aiter/fused_moe.py:3220-3336).
@@ -116,12 +125,15 @@ int b200_moe_quant_1x128(aiter_tensor_t* out, const aiter_tensor_t* input, aiter
  *   w1_scale [E,2I/128,H/128] fp32
  *   a2 [P,I] fp8 and a2_scale [P,I/128] fp32, rows in SORTED order (row p belongs to
  *   sorted_token_ids[p]; rows of pads are zero)
- *   status [1] i32 device word: set non-zero if a bounded device-side wait ran out */
+ *   status [1] i32 device word: set non-zero if a bounded device-side wait ran out
+ *   quant_type: QuantType (csrc/include/aiter_enum.h:16-26). 4/5 (per_1x128/per_128x128) as described; 2
+ *   (per_Token): a1_scale [M], w1_scale [E,2I] (one per output channel), a2 is bf16 [P,I] (SiLU*up, rounded,
+ *   sorted order) and a2_scale is NULL - the caller requantises rows with b200_moe_quant_per_token. */
 int b200_moe_stage1(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale,
                     const aiter_tensor_t* w1, const aiter_tensor_t* w1_scale,
                     const aiter_tensor_t* sorted_token_ids, const aiter_tensor_t* sorted_expert_ids,
                     const aiter_tensor_t* num_valid_ids, aiter_tensor_t* a2, aiter_tensor_t* a2_scale,
-                    aiter_tensor_t* status, void* stream);
+                    aiter_tensor_t* status, int quant_type, void* stream);
 
 /* Stage 2: grouped down GEMM over the sorted blocks, times the route weight, accumulated
  * per token in fp32.  Replaces ck_moe_stage2
@@ -130,13 +142,14 @@ int b200_moe_stage1(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale,
  *   acc [M, col_end-col_begin] fp32, must be zero on entry; receives sum over routes of weight * (a2 . w2)
  *   for the output columns [col_begin, col_end) (multiples of 256; col_end <= 0 means model_dim). Launching
  *   the columns in several ranges lets a caller hand finished ranges to a collective while the next is computed;
- *   sm_margin SMs are then left idle by this launch so that the collective's kernels can run beside it. */
+ *   sm_margin SMs are then left idle by this launch so that the collective's kernels can run beside it.
+ *   quant_type 2 (per_Token): a2_scale [P], w2_scale [E,H]. */
 int b200_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* a2_scale,
                     const aiter_tensor_t* w2, const aiter_tensor_t* w2_scale,
                     const aiter_tensor_t* sorted_token_ids, const aiter_tensor_t* sorted_weights,
                     const aiter_tensor_t* sorted_expert_ids, const aiter_tensor_t* num_valid_ids,
                     aiter_tensor_t* acc, aiter_tensor_t* status, int col_begin, int col_end, int sm_margin,
-                    void* stream);
+                    int quant_type, void* stream);
 
 /* out[M,H] (bf16 or fp16) = round-to-nearest-even(acc[M,H] fp32): the single final rounding of
  * the reference's `out.sum(1).to(dtype)` (aiter/fused_moe.py:3811). */

@@ -13,7 +13,7 @@ import math
 
 import torch
 
-from .moe_oracle import (FP8, biased_grouped_topk_ref, quant_weight_128x128,
+from .moe_oracle import (FP8, biased_grouped_topk_ref, quant_per_token, quant_weight_128x128,
                          softmax_topk_ref)
 
 # name -> dict(M, H, I, E, topk, routing)
@@ -25,7 +25,9 @@ CONFIGS = {
     # DeepSeek-V3 shaped, prefill
     "cfg2": dict(M=8192, H=7168, I=2048, E=256, topk=8, routing="dsv3"),
     # Mixtral-8x7B shaped
-    "cfg3": dict(M=4096, H=4096, I=14336, E=8, topk=2, routing="softmax"),
+    "cfg3": dict(M=4096, H=4096, I=14336, E=8, topk=2, routing="softmax", quant="per_token"),
+    # the tiny layer with per-token activation scales and per-output-channel weight scales
+    "cfg0_pt": dict(M=32, H=1024, I=512, E=8, topk=2, routing="softmax", quant="per_token"),
     # Qwen3-235B-A22B shaped, skewed routing (M is swept by the caller)
     "cfg4": dict(M=1024, H=4096, I=1536, E=128, topk=8, routing="zipf"),
     # DeepSeek-V3 dimensions with few experts: cheap enough for CPU goldens
@@ -63,17 +65,19 @@ def make_routing(kind, M, E, topk, seed, device="cpu"):
     return w.to(device), ids.to(device)
 
 
-def make_weights(E, N, K, seed, device="cpu", experts_per_chunk=1):
+def make_weights(E, N, K, seed, device="cpu", experts_per_chunk=1, per_token=False):
     """[E,N,K] ~ N(0, 1/sqrt(K)) quantised to e4m3 per 128x128 block with
-    scale = amax/448 (op_tests/test_moe_2stage.py:184-208)."""
+    scale = amax/448 (op_tests/test_moe_2stage.py:184-208), or per output channel
+    (scales [E,N,1]) for QuantType.per_Token (:213-214)."""
     g = _gen(seed, device)
     q = torch.empty((E, N, K), dtype=FP8, device=device)
-    s = torch.empty((E, N // 128, K // 128), dtype=torch.float32, device=device)
+    s = (torch.empty((E, N, 1), dtype=torch.float32, device=device) if per_token else
+         torch.empty((E, N // 128, K // 128), dtype=torch.float32, device=device))
     std = 1.0 / math.sqrt(K)
     for e0 in range(0, E, experts_per_chunk):
         e1 = min(E, e0 + experts_per_chunk)
         w = torch.randn((e1 - e0, N, K), generator=g, dtype=torch.float32, device=device) * std
-        qe, se = quant_weight_128x128(w)
+        qe, se = quant_per_token(w) if per_token else quant_weight_128x128(w)
         q[e0:e1] = qe
         s[e0:e1] = se
     return q, s
@@ -91,8 +95,9 @@ def make_config(name, seed=0, device="cpu", M=None, E=None):
         cfg["E"] = E
     M_, H, I, E_, topk = cfg["M"], cfg["H"], cfg["I"], cfg["E"], cfg["topk"]
     x = torch.randn((M_, H), generator=_gen(seed), dtype=torch.float32).to(torch.bfloat16)
-    w1_q, w1_s = make_weights(E_, 2 * I, H, seed + 1, device)
-    w2_q, w2_s = make_weights(E_, H, I, seed + 2, device)
+    pt = cfg.get("quant") == "per_token"
+    w1_q, w1_s = make_weights(E_, 2 * I, H, seed + 1, device, per_token=pt)
+    w2_q, w2_s = make_weights(E_, H, I, seed + 2, device, per_token=pt)
     tw, ti = make_routing(cfg["routing"], M_, E_, topk, seed)
     return dict(x=x.to(device), w1_q=w1_q, w1_scale=w1_s, w2_q=w2_q, w2_scale=w2_s,
                 topk_weight=tw.to(device), topk_ids=ti.to(device), cfg=cfg)

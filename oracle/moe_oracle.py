@@ -110,16 +110,19 @@ def local_expert_ids(topk_ids, expert_mask):
 
 
 # --------------------------------------------------------------------------- GEMM stages
-def _dequant_expert(w_q_e, w_s_e):
-    """aiter/fused_moe.py:3589-3594: w.view(N/128,128,K/128,128) * scale.view(N/128,1,K/128,1)."""
+def _dequant_expert(w_q_e, w_s_e, per_token=False):
+    """aiter/fused_moe.py:3589-3594: w.view(N/128,128,K/128,128) * scale.view(N/128,1,K/128,1);
+    per_Token (:3583-3585): w * scale.view(N, 1)."""
     N, K = w_q_e.shape
+    if per_token:
+        return w_q_e.to(torch.float32) * w_s_e.reshape(N, 1)
     w = w_q_e.to(torch.float32).view(N // 128, 128, K // 128, 128)
     w = w * w_s_e.reshape(N // 128, 1, K // 128, 1)
     return w.view(N, K)
 
 
 def moe_stage1_ref(a1_q, a1_scale, w1_q, w1_scale, topk_weight, topk_ids, inter_dim,
-                   dtype=torch.bfloat16, doweight=False):
+                   dtype=torch.bfloat16, doweight=False, per_token=False):
     """aiter/fused_moe.py:3532-3681, per_1x128/per_128x128 branch, g1u1, SiLU.
 
     a1_q [M,H] e4m3 + a1_scale [M,H/128]; w1_q [E,2I,H] e4m3 + w1_scale
@@ -129,15 +132,18 @@ def moe_stage1_ref(a1_q, a1_scale, w1_q, w1_scale, topk_weight, topk_ids, inter_
     topk = topk_ids.shape[1]
     E, N, _ = w1_q.shape
     hidden = a1_q.to(torch.float32)
-    s = a1_scale.view(M, -1, 1).repeat(1, 1, H // a1_scale.view(M, -1).shape[1]).view(M, -1)
-    hidden = hidden * s
+    if per_token:   # aiter/fused_moe.py:3583-3585: hidden_states * a1_scale with a1_scale [M, 1]
+        hidden = hidden * a1_scale.view(M, 1)
+    else:
+        s = a1_scale.view(M, -1, 1).repeat(1, 1, H // a1_scale.view(M, -1).shape[1]).view(M, -1)
+        hidden = hidden * s
     out = torch.zeros((M, topk, N), dtype=torch.float32)
     for e in range(E):
         mask = topk_ids == e
         if mask.sum():
             tok, _slot = torch.where(mask)
             sub = hidden[tok]
-            w_e = _dequant_expert(w1_q[e], w1_scale[e])
+            w_e = _dequant_expert(w1_q[e], w1_scale[e], per_token)
             act_in = sub @ w_e.transpose(0, 1)
             if doweight:
                 act_in = act_in * topk_weight[mask].view(-1, 1)
@@ -151,7 +157,7 @@ def moe_stage1_ref(a1_q, a1_scale, w1_q, w1_scale, topk_weight, topk_ids, inter_
 
 
 def moe_stage2_ref(a2_q, a2_scale, w2_q, w2_scale, topk_weight, topk_ids,
-                   dtype=torch.bfloat16, doweight=True):
+                   dtype=torch.bfloat16, doweight=True, per_token=False):
     """aiter/fused_moe.py:3684-3811, per_1x128/per_128x128 branch.
 
     a2_q [M,topk,I] e4m3 + a2_scale [M,topk,I/128]; w2_q [E,H,I] + w2_scale
@@ -160,14 +166,17 @@ def moe_stage2_ref(a2_q, a2_scale, w2_q, w2_scale, topk_weight, topk_ids,
     M, topk = topk_ids.shape
     E, H, I = w2_q.shape
     hidden = a2_q.to(torch.float32).view(M, topk, I)
-    s = a2_scale.view(M, topk, -1, 1).repeat(1, 1, 1, 128).view(M, topk, -1)
-    hidden = hidden * s
+    if per_token:   # aiter/fused_moe.py:3729-3731: a2_scale [M, topk, 1]
+        hidden = hidden * a2_scale.view(M, topk, 1)
+    else:
+        s = a2_scale.view(M, topk, -1, 1).repeat(1, 1, 1, 128).view(M, topk, -1)
+        hidden = hidden * s
     out = torch.zeros((M, topk, H), dtype=torch.float32)
     for e in range(E):
         mask = topk_ids == e
         if mask.sum():
             sub = hidden[mask]
-            w_e = _dequant_expert(w2_q[e], w2_scale[e])
+            w_e = _dequant_expert(w2_q[e], w2_scale[e], per_token)
             out[mask] = sub @ w_e.transpose(0, 1)
     if doweight:
         out.mul_(topk_weight.view(M, -1, 1))
@@ -176,7 +185,7 @@ def moe_stage2_ref(a2_q, a2_scale, w2_q, w2_scale, topk_weight, topk_ids,
 
 def fused_moe_ref(x, w1_q, w1_scale, w2_q, w2_scale, topk_weight, topk_ids,
                   expert_mask=None, dtype=torch.bfloat16, return_stages=False,
-                  a1_q=None, a1_scale=None):
+                  a1_q=None, a1_scale=None, per_token=False):
     """The pipeline of op_tests/test_moe_2stage.py (per_128x128 branch):
     a1 quant :237-242 -> torch_moe_stage1 :397-416 -> a2 quant :419-423 ->
     torch_moe_stage2 :448-460.  ``expert_mask`` follows torch_moe
@@ -184,13 +193,14 @@ def fused_moe_ref(x, w1_q, w1_scale, w2_q, w2_scale, topk_weight, topk_ids,
     M, H = x.shape
     I = w2_q.shape[2]
     ids = local_expert_ids(topk_ids, expert_mask)
+    quant = quant_per_token if per_token else quant_1x128   # per_Token: op_tests/test_moe_2stage.py:264,446
     if a1_q is None:
-        a1_q, a1_scale = quant_1x128(x)
-    out1 = moe_stage1_ref(a1_q, a1_scale, w1_q, w1_scale, topk_weight, ids, I, dtype=dtype)
-    a2_q, a2_scale = quant_1x128(out1.view(-1, I))
+        a1_q, a1_scale = quant(x)
+    out1 = moe_stage1_ref(a1_q, a1_scale, w1_q, w1_scale, topk_weight, ids, I, dtype=dtype, per_token=per_token)
+    a2_q, a2_scale = quant(out1.view(-1, I))
     topk = topk_ids.shape[1]
     out = moe_stage2_ref(a2_q.view(M, topk, I), a2_scale.view(M, topk, -1), w2_q, w2_scale,
-                         topk_weight, ids, dtype=dtype)
+                         topk_weight, ids, dtype=dtype, per_token=per_token)
     if return_stages:
         return out, dict(a1_q=a1_q, a1_scale=a1_scale, out1=out1,
                          a2_q=a2_q.view(M, topk, I), a2_scale=a2_scale.view(M, topk, -1))

@@ -266,3 +266,36 @@ def test_stage2_column_ranges_equal_one_launch():
     joined = parts.permute(1, 0, 2).reshape(M, H)
     assert torch.allclose(joined, whole, rtol=1e-5, atol=1e-6)
     assert float(whole.abs().max()) > 0
+
+
+def run_pt(c, **kw):
+    out = aiter_b200.fused_moe(c["x"], c["w1_q"], c["w2_q"], c["topk_weight"], c["topk_ids"],
+                               quant_type=QT.per_Token, w1_scale=c["w1_scale"], w2_scale=c["w2_scale"], **kw)
+    aiter_b200.check_device_status()
+    return out
+
+
+def test_per_token_layer_against_reference_fixture():
+    """QuantType.per_Token (row scales, per-output-channel weight scales) on the tiny layer."""
+    g = load_golden("cfg0_per_token.npz")
+    c = to_dev(inputs.make_config("cfg0_pt", seed=0))
+    a1, a1s = aiter_b200.get_hip_quant(QT.per_Token)(c["x"])
+    assert np.array_equal(a1.cpu().view(torch.uint8).numpy(), g["a1_q"])
+    assert np.array_equal(a1s.cpu().numpy(), g["a1_scale"])
+    assert_parity(run_pt(c), from_bits(g["out"], torch.bfloat16), "cfg0 per_Token")
+    # pre-quantised input with its [M, 1] scale goes the same way
+    out = aiter_b200.fused_moe(a1, c["w1_q"], c["w2_q"], c["topk_weight"], c["topk_ids"], quant_type=QT.per_Token,
+                               w1_scale=c["w1_scale"], w2_scale=c["w2_scale"], a1_scale=a1s)
+    assert_parity(out, from_bits(g["out"], torch.bfloat16), "cfg0 per_Token, fp8 input")
+
+
+def test_mixtral_shape_per_token_sampled():
+    """Config 3: M=4096, H=4096, I=14336, E=8, topk=2, per_Token FP8. Exact check of 24 sampled tokens."""
+    c = to_dev(inputs.make_config("cfg3", seed=0, device=DEV))
+    out = run_pt(c)
+    g = torch.Generator().manual_seed(5)
+    sample = torch.randperm(4096, generator=g)[:24].sort().values.to(DEV)
+    cpu = {k: c[k].cpu() for k in ("w1_q", "w1_scale", "w2_q", "w2_scale")}
+    ref = moe_oracle.fused_moe_ref(c["x"][sample].cpu(), cpu["w1_q"], cpu["w1_scale"], cpu["w2_q"], cpu["w2_scale"],
+                                   c["topk_weight"][sample].cpu(), c["topk_ids"][sample].cpu(), per_token=True)
+    assert_parity(out[sample], ref, "cfg3 Mixtral per_Token, 24 sampled tokens")
