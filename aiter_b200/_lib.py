@@ -45,8 +45,8 @@ _SIGNATURES = {
                                                         ctypes.c_void_p]),
     "b200_moe_quant_1x128": (ctypes.c_int, [_T] * 3 + [ctypes.c_void_p]),
     "b200_moe_quant_per_token": (ctypes.c_int, [_T] * 4 + [ctypes.c_void_p]),
-    "b200_moe_stage1": (ctypes.c_int, [_T] * 10 + [ctypes.c_int, ctypes.c_void_p]),
-    "b200_moe_stage2": (ctypes.c_int, [_T] * 10 + [ctypes.c_int] * 4 + [ctypes.c_void_p]),
+    "b200_moe_stage1": (ctypes.c_int, [_T] * 10 + [ctypes.c_int, _T, ctypes.c_int, ctypes.c_void_p]),
+    "b200_moe_stage2": (ctypes.c_int, [_T] * 10 + [ctypes.c_int] * 5 + [ctypes.c_void_p]),
     "b200_biased_grouped_topk": (ctypes.c_int, [_T] * 4 + [ctypes.c_int] * 3 + [ctypes.c_float, ctypes.c_void_p]),
     "b200_topk_softmax": (ctypes.c_int, [_T] * 4 + [ctypes.c_int, ctypes.c_void_p]),
     "b200_moe_finalize": (ctypes.c_int, [_T] * 2 + [ctypes.c_void_p]),

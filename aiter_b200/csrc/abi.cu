@@ -25,10 +25,10 @@ void launch_quant_1x128(aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*,
 void launch_quant_per_token(aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*, const aiter_tensor_t*, cudaStream_t);
 void launch_moe_stage1(const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*,
                        const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*,
-                       aiter_tensor_t*, aiter_tensor_t*, int, cudaStream_t);
+                       aiter_tensor_t*, aiter_tensor_t*, int, const aiter_tensor_t*, int, cudaStream_t);
 void launch_moe_stage2(const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*,
                        const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*,
-                       aiter_tensor_t*, aiter_tensor_t*, int, int, int, int, cudaStream_t);
+                       aiter_tensor_t*, aiter_tensor_t*, int, int, int, int, int, cudaStream_t);
 
 void launch_biased_grouped_topk(const aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*, int, int,
                                 int, float, cudaStream_t);
@@ -152,12 +152,13 @@ B200_EXPORT int b200_moe_quant_per_token(aiter_tensor_t* out, const aiter_tensor
 B200_EXPORT int b200_moe_stage1(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale, const aiter_tensor_t* w1,
                     const aiter_tensor_t* w1_scale, const aiter_tensor_t* sorted_token_ids,
                     const aiter_tensor_t* sorted_expert_ids, const aiter_tensor_t* num_valid_ids, aiter_tensor_t* a2,
-                    aiter_tensor_t* a2_scale, aiter_tensor_t* status, int quant_type, void* stream) {
+                    aiter_tensor_t* a2_scale, aiter_tensor_t* status, int quant_type,
+                    const aiter_tensor_t* sorted_weights, int activation, void* stream) {
     return safe_call([&] {
         B200_CHECK(a1 != nullptr, "a1 must not be NULL");
         DeviceGuard g(a1->device_id);
         launch_moe_stage1(a1, a1_scale, w1, w1_scale, sorted_token_ids, sorted_expert_ids, num_valid_ids, a2,
-                          a2_scale, status, quant_type, (cudaStream_t)stream);
+                          a2_scale, status, quant_type, sorted_weights, activation, (cudaStream_t)stream);
     });
 }
 
@@ -165,12 +166,12 @@ B200_EXPORT int b200_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* 
                     const aiter_tensor_t* w2_scale, const aiter_tensor_t* sorted_token_ids,
                     const aiter_tensor_t* sorted_weights, const aiter_tensor_t* sorted_expert_ids,
                     const aiter_tensor_t* num_valid_ids, aiter_tensor_t* acc, aiter_tensor_t* status, int col_begin,
-                    int col_end, int sm_margin, int quant_type, void* stream) {
+                    int col_end, int sm_margin, int quant_type, int doweight, void* stream) {
     return safe_call([&] {
         B200_CHECK(a2 != nullptr, "a2 must not be NULL");
         DeviceGuard g(a2->device_id);
         launch_moe_stage2(a2, a2_scale, w2, w2_scale, sorted_token_ids, sorted_weights, sorted_expert_ids,
-                          num_valid_ids, acc, status, col_begin, col_end, sm_margin, quant_type, (cudaStream_t)stream);
+                          num_valid_ids, acc, status, col_begin, col_end, sm_margin, quant_type, doweight, (cudaStream_t)stream);
     });
 }
 

@@ -87,6 +87,8 @@ struct GemmParams {
     float* a2_scale;         // stage 1 out [P, I/128]
     float* acc;              // stage 2 out [M, H] fp32
     int* status;
+    int use_weight;          // multiply this stage's GEMM result by the route weight (sorted_w)
+    int act;                 // stage 1 activation: 0 = SiLU, 1 = GELU (erf form)
 };
 
 // torch: silu(x) = x / (1 + exp(-x)) in fp32, then * up (aiter/fused_moe.py:3676).
@@ -99,6 +101,12 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
     const float q = g * y;
     return fmaf(fmaf(-q, d, g), y, q) * u;
 }
+
+// torch: gelu(x) = 0.5 * x * (1 + erf(x / sqrt(2))) (the reference's get_torch_act(Gelu) = F.gelu), then * up
+__device__ __forceinline__ float gelu_mul(float g, float u) {
+    return 0.5f * g * (1.0f + erff(g * 0.70710678118654752440f)) * u;
+}
+__device__ __forceinline__ float act_mul(int act, float g, float u) { return act == 1 ? gelu_mul(g, u) : silu_mul(g, u); }
 
 // Correctly rounded a / b given rb = RN(1/b): two FMA residual corrections (the first makes the
 // quotient faithful, the second then rounds it correctly), valid while nothing over- or underflows.
@@ -308,19 +316,19 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
         if ((int)blockIdx.x < total_tiles) {
             const int prow0 = ((int)blockIdx.x / p.n_tiles) * BM + r;
             tok_next = p.sorted_ids[prow0] & 0xFFFFFF;
-            if (STAGE == 2) wgt_next = p.sorted_w[prow0];
+            if (p.use_weight) wgt_next = p.sorted_w[prow0];
         }
         for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, tile_par ^= 1u) {
             const int blk = t / p.n_tiles, nt = t - blk * p.n_tiles + p.nt0;
             const int prow = blk * BM + r;
             const int tok = tok_next;
             const bool valid = tok < tokens;
-            // stage 2: the route weight rides on the per-step scales (pads get 0)
-            const float wgt = (STAGE == 2) ? (valid ? wgt_next : 0.f) : 1.f;
+            // the route weight (stage 2, or stage 1 with doweight_stage1) rides on the per-step scales
+            const float wgt = p.use_weight ? (valid ? wgt_next : 0.f) : 1.f;
             if (t + (int)gridDim.x < total_tiles) {
                 const int prow1 = ((t + (int)gridDim.x) / p.n_tiles) * BM + r;
                 tok_next = p.sorted_ids[prow1] & 0xFFFFFF;
-                if (STAGE == 2) wgt_next = p.sorted_w[prow1];
+                if (p.use_weight) wgt_next = p.sorted_w[prow1];
             }
             // a warp whose 32 rows are all padding (decode: most of them) leaves its accumulators at 0
             const bool warp_live = __any_sync(0xffffffffu, valid);
@@ -337,7 +345,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                 if (!(ok = ptx::mbar_wait<kEpilogueSleepNs>(tfull_bar(ts), tph, abort_flag))) break;
                 ptx::tc_fence_after();
                 const uint32_t slot = it % kScaleSlots;
-                const float sa = (STAGE == 2) ? scale_a[slot * BM + r] * wgt : scale_a[slot * BM + r];
+                const float sa = p.use_weight ? scale_a[slot * BM + r] * wgt : scale_a[slot * BM + r];
                 const float s0 = PT ? sa : sa * scale_w[slot * 2], s1 = PT ? sa : sa * scale_w[slot * 2 + 1];
                 const float2 s0v = make_float2(s0, s0), s1v = make_float2(s1, s1);
                 const uint32_t ta = lane_addr + ts * BN + half * 64;
@@ -386,7 +394,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                 uint32_t w[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
-                    __nv_bfloat162 h = __floats2bfloat162_rn(silu_mul(acc[j].x, acc[32 + j].x), silu_mul(acc[j].y, acc[32 + j].y));
+                    __nv_bfloat162 h = __floats2bfloat162_rn(act_mul(p.act, acc[j].x, acc[32 + j].x), act_mul(p.act, acc[j].y, acc[32 + j].y));
                     w[j] = *reinterpret_cast<uint32_t*>(&h);
                 }
                 uint4* dst = reinterpret_cast<uint4*>(p.a2 + ((size_t)prow * p.inter + nt * 128 + half * 64) * 2);
@@ -398,8 +406,8 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                 float amax = 0.f;
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {   // acc[j] is overwritten by the two activations it feeds
-                    float h0 = __bfloat162float(__float2bfloat16_rn(silu_mul(acc[j].x, acc[32 + j].x)));
-                    float h1 = __bfloat162float(__float2bfloat16_rn(silu_mul(acc[j].y, acc[32 + j].y)));
+                    float h0 = __bfloat162float(__float2bfloat16_rn(act_mul(p.act, acc[j].x, acc[32 + j].x)));
+                    float h1 = __bfloat162float(__float2bfloat16_rn(act_mul(p.act, acc[j].y, acc[32 + j].y)));
                     acc[j] = make_float2(h0, h1);
                     amax = fmaxf(amax, fmaxf(fabsf(h0), fabsf(h1)));
                 }
@@ -545,7 +553,13 @@ void launch_gemm(const CUtensorMap& tmap, const GemmParams& p, int64_t max_tiles
 void launch_moe_stage1(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale, const aiter_tensor_t* w1,
                        const aiter_tensor_t* w1_scale, const aiter_tensor_t* sorted_ids,
                        const aiter_tensor_t* sorted_eids, const aiter_tensor_t* num_valid, aiter_tensor_t* a2,
-                       aiter_tensor_t* a2_scale, aiter_tensor_t* status, int quant_type, cudaStream_t stream) {
+                       aiter_tensor_t* a2_scale, aiter_tensor_t* status, int quant_type,
+                       const aiter_tensor_t* sorted_w, int activation, cudaStream_t stream) {
+    B200_CHECK(activation == 0 || activation == 1, "activation must be Silu (0) or Gelu (1), got ", activation);
+    if (sorted_w) {
+        check_tensor(sorted_w, "sorted_weights", AITER_DTYPE_fp32, 1);
+        B200_CHECK(sorted_w->numel_ >= sorted_ids->numel_, "sorted_weights must cover sorted_token_ids");
+    }
     // quant_type: QuantType of the reference (csrc/include/aiter_enum.h:16-26): 4/5 = block scale, 2 = per_Token
     B200_CHECK(quant_type == 4 || quant_type == 5 || quant_type == 2,
                "quant_type must be per_1x128 (4), per_128x128 (5) or per_Token (2), got ", quant_type);
@@ -601,6 +615,9 @@ void launch_moe_stage1(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale,
     p.a2 = (uint8_t*)a2->ptr;
     p.a2_scale = pt ? nullptr : (float*)a2_scale->ptr;
     p.status = (int*)status->ptr;
+    p.sorted_w = sorted_w ? (const float*)sorted_w->ptr : nullptr;
+    p.use_weight = sorted_w != nullptr;   // doweight_stage1 (aiter/fused_moe.py:3651-3652)
+    p.act = activation;
     CUtensorMap tmap = make_weight_map(w1->ptr, (uint64_t)(E * N2), (uint64_t)H);
     const int64_t max_tiles = ((int64_t)sorted_ids->numel_ / BM) * p.n_tiles;
     if (pt) launch_gemm<1, true>(tmap, p, max_tiles, a1->device_id, stream);
@@ -611,7 +628,7 @@ void launch_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* a2_scale,
                        const aiter_tensor_t* w2_scale, const aiter_tensor_t* sorted_ids,
                        const aiter_tensor_t* sorted_w, const aiter_tensor_t* sorted_eids,
                        const aiter_tensor_t* num_valid, aiter_tensor_t* acc, aiter_tensor_t* status,
-                       int col_begin, int col_end, int sm_margin, int quant_type, cudaStream_t stream) {
+                       int col_begin, int col_end, int sm_margin, int quant_type, int doweight, cudaStream_t stream) {
     B200_CHECK(quant_type == 4 || quant_type == 5 || quant_type == 2,
                "quant_type must be per_1x128 (4), per_128x128 (5) or per_Token (2), got ", quant_type);
     const bool pt = quant_type == 2;
@@ -670,6 +687,7 @@ void launch_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* a2_scale,
     p.inter = (int)I;
     p.acc = (float*)acc->ptr;
     p.status = (int*)status->ptr;
+    p.use_weight = doweight != 0;
     CUtensorMap tmap = make_weight_map(w2->ptr, (uint64_t)(E * H), (uint64_t)I);
     const int64_t max_tiles = ((int64_t)sorted_ids->numel_ / BM) * p.n_tiles;
     if (pt) launch_gemm<2, true>(tmap, p, max_tiles, a2->device_id, stream, sm_margin);

@@ -191,7 +191,8 @@ def _mark(timers, name):
 
 def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, w1_scale, w2_scale,
                      a1_scale, num_local_tokens, dtype, return_intermediates=False, timers=None,
-                     stage2_chunks=1, on_chunk=None, sm_margin=0, quant_type=QuantType.per_1x128):
+                     stage2_chunks=1, on_chunk=None, sm_margin=0, quant_type=QuantType.per_1x128,
+                     activation=ActivationType.Silu, doweight_stage1=False):
     """sort -> a1 quant -> stage 1 -> stage 2 -> final rounding (the 2-stage flow of
     aiter/fused_moe.py:2979-3368 with the requant fused into stage 1).
 
@@ -215,6 +216,9 @@ def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, 
         num_local_tokens, 0, False, want_moe_buf=False)
     _mark(timers, "quant")
     per_token = QuantType(quant_type) == QuantType.per_Token
+    act = int(ActivationType(activation))
+    w_stage1 = sorted_weights if doweight_stage1 else None   # aiter/fused_moe.py:3651-3652
+    dw2 = 0 if doweight_stage1 else 1
     qt = int(QuantType.per_Token if per_token else QuantType.per_1x128)
     if hidden_states.dtype == dtypes.fp8:
         a1, a1_s = hidden_states.contiguous(), a1_scale.contiguous().view(M, -1)
@@ -231,7 +235,7 @@ def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, 
         # so the requantisation is a pass of its own over the valid rows (num_valid_ids[0] on the device)
         a2_bf16 = torch.empty((P, inter_dim), dtype=dtypes.bf16, device=device)
         _lib.call("b200_moe_stage1", a1, a1_s, w1, w1_scale, sorted_ids, sorted_expert_ids, num_valid_ids,
-                  a2_bf16, None, status, qt, device=device)
+                  a2_bf16, None, status, qt, w_stage1, act, device=device)
         _mark(timers, "requant")
         a2 = torch.empty((P, inter_dim), dtype=dtypes.fp8, device=device)
         a2_s = torch.empty((P,), dtype=dtypes.fp32, device=device)
@@ -240,7 +244,7 @@ def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, 
         a2 = torch.empty((P, inter_dim), dtype=dtypes.fp8, device=device)
         a2_s = torch.empty((P, inter_dim // 128), dtype=dtypes.fp32, device=device)
         _lib.call("b200_moe_stage1", a1, a1_s, w1, w1_scale, sorted_ids, sorted_expert_ids, num_valid_ids,
-                  a2, a2_s, status, qt, device=device)
+                  a2, a2_s, status, qt, w_stage1, act, device=device)
     _mark(timers, "zero")
     if stage2_chunks > 1:
         if dtype is not None or model_dim % (256 * stage2_chunks) != 0:
@@ -250,7 +254,7 @@ def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, 
         _mark(timers, "stage2")
         for c in range(stage2_chunks):
             _lib.call("b200_moe_stage2", a2, a2_s, w2, w2_scale, sorted_ids, sorted_weights, sorted_expert_ids,
-                      num_valid_ids, acc[c], status, c * hc, (c + 1) * hc, int(sm_margin), qt, device=device)
+                      num_valid_ids, acc[c], status, c * hc, (c + 1) * hc, int(sm_margin), qt, dw2, device=device)
             if on_chunk is not None:
                 on_chunk(c, acc[c])
         _mark(timers, "end")
@@ -258,7 +262,7 @@ def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, 
     acc = torch.zeros((M, model_dim), dtype=dtypes.fp32, device=device)
     _mark(timers, "stage2")
     _lib.call("b200_moe_stage2", a2, a2_s, w2, w2_scale, sorted_ids, sorted_weights, sorted_expert_ids,
-              num_valid_ids, acc, status, 0, 0, 0, qt, device=device)
+              num_valid_ids, acc, status, 0, 0, 0, qt, dw2, device=device)
     if dtype is None:        # caller wants the fp32 sums (expert parallelism reduces them across ranks first)
         _mark(timers, "end")
         return acc
@@ -324,10 +328,10 @@ def fused_moe(
         raise NotImplementedError(
             f"fused_moe: quant_type={QuantType(quant_type)!r} is not supported; this build covers "
             "QuantType.per_1x128 / per_128x128 (FP8 block scale) and QuantType.per_Token (FP8)")
-    if ActivationType(activation) != ActivationType.Silu:
-        raise NotImplementedError(f"fused_moe: activation={ActivationType(activation)!r} is not supported (Silu only)")
+    if ActivationType(activation) not in (ActivationType.Silu, ActivationType.Gelu):
+        raise NotImplementedError(f"fused_moe: activation={ActivationType(activation)!r} is not supported (Silu, Gelu)")
     _check_unsupported(
-        doweight_stage1=(bool(doweight_stage1), False), a2_scale=(a2_scale, None),
+        a2_scale=(a2_scale, None),
         hidden_pad=(hidden_pad, 0), intermediate_pad=(intermediate_pad, 0), bias1=(bias1, None),
         bias2=(bias2, None), splitk=(splitk or 0, 0), swiglu_limit=(swiglu_limit, None),
         beta=(beta, None), linear_beta=(linear_beta, None), shared_w1=(shared_w1, None),
@@ -369,4 +373,5 @@ def fused_moe(
         raise ValueError("fused_moe: topk_ids must be int32")
     return fused_moe_stages(hidden_states, w1.contiguous(), w2.contiguous(), topk_weight, topk_ids,
                             expert_mask, w1_scale.contiguous(), w2_scale.contiguous(), a1_scale,
-                            num_local_tokens, dtype, quant_type=quant_type)
+                            num_local_tokens, dtype, quant_type=quant_type, activation=activation,
+                            doweight_stage1=bool(doweight_stage1))

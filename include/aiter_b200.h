@@ -128,12 +128,15 @@ int b200_moe_quant_per_token(aiter_tensor_t* out, const aiter_tensor_t* input, a
  *   status [1] i32 device word: set non-zero if a bounded device-side wait ran out
  *   quant_type: QuantType (csrc/include/aiter_enum.h:16-26). 4/5 (per_1x128/per_128x128) as described; 2
  *   (per_Token): a1_scale [M], w1_scale [E,2I] (one per output channel), a2 is bf16 [P,I] (SiLU*up, rounded,
- *   sorted order) and a2_scale is NULL - the caller requantises rows with b200_moe_quant_per_token. */
+ *   sorted order) and a2_scale is NULL - the caller requantises rows with b200_moe_quant_per_token.
+ *   sorted_weights: NULL, or the route weights to multiply the GEMM result with before the activation
+ *   (doweight_stage1, aiter/fused_moe.py:3651-3652); activation: ActivationType, 0 = Silu, 1 = Gelu. */
 int b200_moe_stage1(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale,
                     const aiter_tensor_t* w1, const aiter_tensor_t* w1_scale,
                     const aiter_tensor_t* sorted_token_ids, const aiter_tensor_t* sorted_expert_ids,
                     const aiter_tensor_t* num_valid_ids, aiter_tensor_t* a2, aiter_tensor_t* a2_scale,
-                    aiter_tensor_t* status, int quant_type, void* stream);
+                    aiter_tensor_t* status, int quant_type, const aiter_tensor_t* sorted_weights, int activation,
+                    void* stream);
 
 /* Stage 2: grouped down GEMM over the sorted blocks, times the route weight, accumulated
  * per token in fp32.  Replaces ck_moe_stage2
@@ -143,13 +146,14 @@ int b200_moe_stage1(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale,
  *   for the output columns [col_begin, col_end) (multiples of 256; col_end <= 0 means model_dim). Launching
  *   the columns in several ranges lets a caller hand finished ranges to a collective while the next is computed;
  *   sm_margin SMs are then left idle by this launch so that the collective's kernels can run beside it.
- *   quant_type 2 (per_Token): a2_scale [P], w2_scale [E,H]. */
+ *   quant_type 2 (per_Token): a2_scale [P], w2_scale [E,H]. doweight 0 leaves the route weight out
+ *   (it was applied in stage 1). */
 int b200_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* a2_scale,
                     const aiter_tensor_t* w2, const aiter_tensor_t* w2_scale,
                     const aiter_tensor_t* sorted_token_ids, const aiter_tensor_t* sorted_weights,
                     const aiter_tensor_t* sorted_expert_ids, const aiter_tensor_t* num_valid_ids,
                     aiter_tensor_t* acc, aiter_tensor_t* status, int col_begin, int col_end, int sm_margin,
-                    int quant_type, void* stream);
+                    int quant_type, int doweight, void* stream);
 
 /* out[M,H] (bf16 or fp16) = round-to-nearest-even(acc[M,H] fp32): the single final rounding of
  * the reference's `out.sum(1).to(dtype)` (aiter/fused_moe.py:3811). */

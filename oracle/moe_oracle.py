@@ -122,7 +122,7 @@ def _dequant_expert(w_q_e, w_s_e, per_token=False):
 
 
 def moe_stage1_ref(a1_q, a1_scale, w1_q, w1_scale, topk_weight, topk_ids, inter_dim,
-                   dtype=torch.bfloat16, doweight=False, per_token=False):
+                   dtype=torch.bfloat16, doweight=False, per_token=False, activation="silu"):
     """aiter/fused_moe.py:3532-3681, per_1x128/per_128x128 branch, g1u1, SiLU.
 
     a1_q [M,H] e4m3 + a1_scale [M,H/128]; w1_q [E,2I,H] e4m3 + w1_scale
@@ -148,11 +148,12 @@ def moe_stage1_ref(a1_q, a1_scale, w1_q, w1_scale, topk_weight, topk_ids, inter_
             if doweight:
                 act_in = act_in * topk_weight[mask].view(-1, 1)
             out[mask] = act_in
+    act = F.gelu if activation == "gelu" else F.silu   # aiter.get_torch_act (aiter/fused_moe.py:3665)
     if N == 2 * inter_dim:
         gate, up = out.split([inter_dim, inter_dim], dim=-1)
-        out = F.silu(gate) * up
+        out = act(gate) * up
     else:
-        out = F.silu(out)
+        out = act(out)
     return out.to(dtype)
 
 
@@ -185,7 +186,8 @@ def moe_stage2_ref(a2_q, a2_scale, w2_q, w2_scale, topk_weight, topk_ids,
 
 def fused_moe_ref(x, w1_q, w1_scale, w2_q, w2_scale, topk_weight, topk_ids,
                   expert_mask=None, dtype=torch.bfloat16, return_stages=False,
-                  a1_q=None, a1_scale=None, per_token=False):
+                  a1_q=None, a1_scale=None, per_token=False, activation="silu",
+                  doweight_stage1=False):
     """The pipeline of op_tests/test_moe_2stage.py (per_128x128 branch):
     a1 quant :237-242 -> torch_moe_stage1 :397-416 -> a2 quant :419-423 ->
     torch_moe_stage2 :448-460.  ``expert_mask`` follows torch_moe
@@ -196,11 +198,12 @@ def fused_moe_ref(x, w1_q, w1_scale, w2_q, w2_scale, topk_weight, topk_ids,
     quant = quant_per_token if per_token else quant_1x128   # per_Token: op_tests/test_moe_2stage.py:264,446
     if a1_q is None:
         a1_q, a1_scale = quant(x)
-    out1 = moe_stage1_ref(a1_q, a1_scale, w1_q, w1_scale, topk_weight, ids, I, dtype=dtype, per_token=per_token)
+    out1 = moe_stage1_ref(a1_q, a1_scale, w1_q, w1_scale, topk_weight, ids, I, dtype=dtype, per_token=per_token,
+                          activation=activation, doweight=doweight_stage1)
     a2_q, a2_scale = quant(out1.view(-1, I))
     topk = topk_ids.shape[1]
     out = moe_stage2_ref(a2_q.view(M, topk, I), a2_scale.view(M, topk, -1), w2_q, w2_scale,
-                         topk_weight, ids, dtype=dtype, per_token=per_token)
+                         topk_weight, ids, dtype=dtype, per_token=per_token, doweight=not doweight_stage1)
     if return_stages:
         return out, dict(a1_q=a1_q, a1_scale=a1_scale, out1=out1,
                          a2_q=a2_q.view(M, topk, I), a2_scale=a2_scale.view(M, topk, -1))

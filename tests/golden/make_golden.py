@@ -16,6 +16,7 @@ Fixtures (numpy ``.npz``; bf16 stored as its uint16 bit pattern, e4m3 as uint8):
   cfg0_ep2.npz        the same layer split over 2 expert-parallel ranks (local ids + mask)
   dsv3_slice.npz      DeepSeek-V3 dimensions with 8 experts (M=16,H=7168,I=2048,topk=8)
   cfg0_per_token.npz  the tiny layer with QuantType.per_Token (row scales, per-output-channel weight scales)
+  cfg0_variants.npz   the tiny layer with Gelu and/or doweight_stage1
   routing_dsv3.npz    biased_grouped_topk_torch (8 groups, top-4 groups, top-8, x2.5)
 """
 
@@ -190,6 +191,26 @@ def main():
     c0, r0 = layer_case(ref, "cfg0", "cfg0.npz")
     layer_case(ref, "dsv3_slice", "dsv3_slice.npz")
     layer_case(ref, "cfg0_pt", "cfg0_per_token.npz")
+
+    # ---- activation / weighting variants on the tiny layer (aiter/fused_moe.py:3651-3652, 3665-3681) ----
+    var = {}
+    for tag, act_ref, act, dw1 in (("gelu", ref.ActivationType.Gelu, "gelu", False),
+                                   ("doweight1", ref.ActivationType.Silu, "silu", True),
+                                   ("gelu_doweight1", ref.ActivationType.Gelu, "gelu", True)):
+        QT = ref.QuantType.per_128x128
+        M, topk = c0["topk_ids"].shape
+        o1 = ref.torch_moe_stage1(r0["a1_q"], c0["w1_q"], c0["w2_q"], c0["topk_weight"], c0["topk_ids"],
+                                  dtype=torch.bfloat16, activation=act_ref, quant_type=QT, a1_scale=r0["a1_scale"],
+                                  w1_scale=c0["w1_scale"], doweight=dw1)
+        q2, s2 = ref.pertoken_quant(o1.view(M, -1, 128), quant_dtype=FP8)
+        o = ref.torch_moe_stage2(q2.view(M, topk, -1), c0["w1_q"], c0["w2_q"], c0["topk_weight"], c0["topk_ids"],
+                                 dtype=torch.bfloat16, quant_type=QT, w2_scale=c0["w2_scale"],
+                                 a2_scale=s2.view(M, topk, -1), doweight=not dw1)
+        mine = moe_oracle.fused_moe_ref(c0["x"], c0["w1_q"], c0["w1_scale"], c0["w2_q"], c0["w2_scale"],
+                                        c0["topk_weight"], c0["topk_ids"], activation=act, doweight_stage1=dw1)
+        assert same(o, mine), tag
+        var[tag] = bits(o)
+    save("cfg0_variants.npz", **var)
 
     # ---- expert parallel, 2 ranks (masking as in aiter/fused_moe.py:3467-3470) -----------
     E = c0["cfg"]["E"]

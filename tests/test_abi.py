@@ -87,11 +87,11 @@ def test_unsupported_options_are_named():
     with pytest.raises(NotImplementedError, match="quant_type"):
         aiter_b200.fused_moe(x, w1, w2, tw, ti, quant_type=QT.per_1x32)
     with pytest.raises(NotImplementedError, match="activation"):
-        aiter_b200.fused_moe(x, w1, w2, tw, ti, quant_type=QT.per_1x128, activation=AT.Gelu)
+        aiter_b200.fused_moe(x, w1, w2, tw, ti, quant_type=QT.per_1x128, activation=AT.Swiglu)
     with pytest.raises(NotImplementedError, match="bias1"):
         aiter_b200.fused_moe(x, w1, w2, tw, ti, quant_type=QT.per_1x128, bias1=torch.zeros(1))
-    with pytest.raises(NotImplementedError, match="doweight_stage1"):
-        aiter_b200.fused_moe(x, w1, w2, tw, ti, quant_type=QT.per_128x128, doweight_stage1=True)
+    with pytest.raises(NotImplementedError, match="splitk"):
+        aiter_b200.fused_moe(x, w1, w2, tw, ti, quant_type=QT.per_128x128, splitk=2)
     with pytest.raises(RuntimeError, match="CUDA"):
         aiter_b200.fused_moe(x, w1, w2, tw, ti, quant_type=QT.per_1x128,
                              w1_scale=torch.ones(1), w2_scale=torch.ones(1))

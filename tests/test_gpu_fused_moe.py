@@ -299,3 +299,13 @@ def test_mixtral_shape_per_token_sampled():
     ref = moe_oracle.fused_moe_ref(c["x"][sample].cpu(), cpu["w1_q"], cpu["w1_scale"], cpu["w2_q"], cpu["w2_scale"],
                                    c["topk_weight"][sample].cpu(), c["topk_ids"][sample].cpu(), per_token=True)
     assert_parity(out[sample], ref, "cfg3 Mixtral per_Token, 24 sampled tokens")
+
+
+@pytest.mark.parametrize("tag,act,dw1", [("gelu", "Gelu", False), ("doweight1", "Silu", True),
+                                         ("gelu_doweight1", "Gelu", True)])
+def test_activation_and_stage1_weighting_variants(tag, act, dw1):
+    """Gelu and doweight_stage1 (route weight applied to the stage-1 GEMM result, before the activation)."""
+    g = load_golden("cfg0_variants.npz")
+    c = to_dev(inputs.make_config("cfg0", seed=0))
+    out = run(c, activation=getattr(aiter_b200.ActivationType, act), doweight_stage1=dw1)
+    assert_parity(out, from_bits(g[tag], torch.bfloat16), tag)

@@ -123,3 +123,13 @@ def test_routing_dsv3():
     # every token: 8 distinct experts from at most 4 groups of 32
     assert all(len(set(r.tolist())) == 8 for r in ids)
     assert all(len(set((r // 32).tolist())) <= 4 for r in ids)
+
+
+def test_layer_variants_gelu_doweight():
+    g = load_golden("cfg0_variants.npz")
+    c = inputs.make_config("cfg0", seed=0)
+    for tag, act, dw1 in (("gelu", "gelu", False), ("doweight1", "silu", True), ("gelu_doweight1", "gelu", True)):
+        out = moe_oracle.fused_moe_ref(c["x"], c["w1_q"], c["w1_scale"], c["w2_q"], c["w2_scale"], c["topk_weight"],
+                                       c["topk_ids"], activation=act, doweight_stage1=dw1)
+        s = moe_oracle.error_stats(out, from_bits(g[tag], BF16))
+        assert s["max_abs_over_rms"] <= 0.02 and s["frac_within"] >= 0.999, (tag, s)
