@@ -375,3 +375,43 @@ def fused_moe(
                             expert_mask, w1_scale.contiguous(), w2_scale.contiguous(), a1_scale,
                             num_local_tokens, dtype, quant_type=quant_type, activation=activation,
                             doweight_stage1=bool(doweight_stage1))
+
+
+# ------------------------------------------------------------------------------------- torch integration
+def shuffle_weight(x, layout=(16, 16), use_int4=False, is_guinterleave=False, gate_up=False, pad_k_to=0):
+    """Weight prepack hook with the signature of aiter/ops/shuffle.py:148-209.
+
+    The reference permutes weights into 16x16 MFMA tiles and marks them ``is_shuffled``; on B200 the
+    TMA reads the plain K-major ``[E, N, K]`` rows, so the prepack is the identity. The attribute
+    protocol is kept (``fused_moe`` in the reference reads it, aiter/fused_moe.py:747) so loaders that
+    call ``shuffle_weight`` once at model load keep working."""
+    if use_int4 or is_guinterleave or pad_k_to:
+        raise NotImplementedError("shuffle_weight: int4 / gate-up interleave / K padding are not supported")
+    x.is_shuffled = True
+    return x
+
+
+def _fused_moe_fake(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask=None, activation=0, quant_type=0,
+                    doweight_stage1=False, w1_scale=None, w2_scale=None, a1_scale=None, num_local_tokens=None,
+                    dtype=None):
+    """Shape/dtype propagation of aiter/fused_moe.py:579-619: empty((M, model_dim), dtype)."""
+    M = topk_ids.shape[0]
+    out_dtype = dtype if dtype is not None else (dtypes.bf16 if hidden_states.dtype == dtypes.fp8 else hidden_states.dtype)
+    return torch.empty((M, w2.shape[1]), dtype=out_dtype, device=topk_ids.device)
+
+
+@torch.library.custom_op("aiter_b200::fused_moe_", mutates_args=(), device_types="cuda")
+def fused_moe_(hidden_states: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, topk_weight: torch.Tensor,
+               topk_ids: torch.Tensor, expert_mask: torch.Tensor | None = None, activation: int = 0,
+               quant_type: int = 0, doweight_stage1: bool = False, w1_scale: torch.Tensor | None = None,
+               w2_scale: torch.Tensor | None = None, a1_scale: torch.Tensor | None = None,
+               num_local_tokens: torch.Tensor | None = None, dtype: torch.dtype | None = None) -> torch.Tensor:
+    """The layer as a registered torch operator (enums as ints, like the reference's ``fused_moe_``,
+    aiter/fused_moe.py:622-695), so that graphs traced by torch.compile carry it as one opaque call."""
+    return fused_moe(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask=expert_mask,
+                     activation=ActivationType(activation), quant_type=QuantType(quant_type),
+                     doweight_stage1=doweight_stage1, w1_scale=w1_scale, w2_scale=w2_scale, a1_scale=a1_scale,
+                     num_local_tokens=num_local_tokens, dtype=dtype)
+
+
+fused_moe_.register_fake(_fused_moe_fake)

@@ -381,7 +381,20 @@ def main():
         us = statistics.median(td) * 1e3
         gbs = algorithmic_bytes(M_DECODE, n_act) / (us * 1e-6) / 1e9
         kbd = kernel_breakdown(fm, (dxd, w1_q, w2_q, dtwd, dtid, None, w1_s, w2_s, None, None, torch.bfloat16))
+        # the same layer replayed from a CUDA graph (how serving stacks run decode): no launch gaps
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            step_decode()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        with torch.cuda.graph(graph):
+            step_decode()
+        tg = timed(graph.replay, max(args.steps, 20), args.warmup, sync)
+        us_graph = statistics.median(tg) * 1e3
         line["decode"] = {"metric": "DSV3 FP8-blockscale fused_moe us/layer (M=64)", "value": us, "unit": "us",
+                          "graph_replay_us": us_graph,
+                          "graph_replay_frac_of_hbm": algorithmic_bytes(M_DECODE, n_act) / (us_graph * 1e-6) / 1e9 / pk["hbm_gbs"],
                           "active_experts": n_act, "kernels_ms": {k: round(v, 4) for k, v in kbd.items()},
                           "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s",
                                        "frac": gbs / pk["hbm_gbs"], "traffic": None,

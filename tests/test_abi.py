@@ -106,3 +106,22 @@ def test_enums_match_reference_values():
     assert (AT.No, AT.Silu, AT.Gelu, AT.Swiglu, AT.Situv2) == (-1, 0, 1, 2, 3)
     assert [q.value for q in QT] == list(range(8))
     assert QT.per_1x128 == 4 and QT.per_128x128 == 5
+
+
+def test_registered_operator_fake_and_shuffle_hook():
+    """The torch operator propagates shapes on meta tensors (aiter/fused_moe.py:579-619) and
+    shuffle_weight keeps the is_shuffled protocol (aiter/ops/shuffle.py:148-209, aiter/fused_moe.py:747)."""
+    x = torch.empty((4, 256), dtype=torch.bfloat16, device="meta")
+    w1 = torch.empty((2, 512, 256), dtype=torch.float8_e4m3fn, device="meta")
+    w2 = torch.empty((2, 256, 256), dtype=torch.float8_e4m3fn, device="meta")
+    tw = torch.empty((4, 1), device="meta")
+    ti = torch.empty((4, 1), dtype=torch.int32, device="meta")
+    out = torch.ops.aiter_b200.fused_moe_(x, w1, w2, tw, ti, None, 0, 4, False, None, None, None, None, None)
+    assert out.shape == (4, 256) and out.dtype == torch.bfloat16
+    out = torch.ops.aiter_b200.fused_moe_(x.to(torch.float8_e4m3fn), w1, w2, tw, ti, None, 0, 4, False, None, None,
+                                          None, None, torch.float16)
+    assert out.dtype == torch.float16
+    w = torch.zeros((2, 128, 128), dtype=torch.float8_e4m3fn)
+    assert aiter_b200.shuffle_weight(w) is w and w.is_shuffled
+    with pytest.raises(NotImplementedError):
+        aiter_b200.shuffle_weight(w, use_int4=True)

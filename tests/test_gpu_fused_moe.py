@@ -309,3 +309,13 @@ def test_activation_and_stage1_weighting_variants(tag, act, dw1):
     c = to_dev(inputs.make_config("cfg0", seed=0))
     out = run(c, activation=getattr(aiter_b200.ActivationType, act), doweight_stage1=dw1)
     assert_parity(out, from_bits(g[tag], torch.bfloat16), tag)
+
+
+def test_registered_operator_matches_function():
+    c = to_dev(inputs.make_config("cfg0", seed=4))
+    ref = run(c)
+    out = torch.ops.aiter_b200.fused_moe_(c["x"], c["w1_q"], c["w2_q"], c["topk_weight"], c["topk_ids"], None,
+                                          int(aiter_b200.ActivationType.Silu), int(QT.per_1x128), False,
+                                          c["w1_scale"], c["w2_scale"], None, None, None)
+    s = moe_oracle.error_stats(out, ref.cpu())
+    assert s["n_diff"] <= 1e-3 * s["numel"] and s["max_abs_over_rms"] <= MAX_ABS_OVER_RMS, s
