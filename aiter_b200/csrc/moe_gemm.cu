@@ -116,10 +116,10 @@ __device__ __forceinline__ float div_rn_by(float a, float b, float rb) {
     return fmaf(fmaf(-q, b, a), rb, q);
 }
 
-// acc[0..15] += v[0..31] * s with packed fp32x2 FMAs (one instruction per column pair)
-__device__ __forceinline__ void fold32(float2* acc, const uint32_t* v, float2 s) {
+// acc[0..7] += v[0..15] * s with packed fp32x2 FMAs (one instruction per column pair)
+__device__ __forceinline__ void fold16(float2* acc, const uint32_t* v, float2 s) {
 #pragma unroll
-    for (int j = 0; j < 16; ++j)
+    for (int j = 0; j < 8; ++j)
         acc[j] = __ffma2_rn(make_float2(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1])), s, acc[j]);
 }
 
@@ -349,25 +349,26 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                 const float s0 = PT ? sa : sa * scale_w[slot * 2], s1 = PT ? sa : sa * scale_w[slot * 2 + 1];
                 const float2 s0v = make_float2(s0, s0), s1v = make_float2(s1, s1);
                 const uint32_t ta = lane_addr + ts * BN + half * 64;
-                // Four 32-column chunks: load + wait, then 16 packed FMAs.  The packed fp32x2 FMAs matter:
+                // load + wait, then packed FMAs.  The packed fp32x2 FMAs matter:
                 // they need half the issue slots of scalar FMAs, and with scalar FMAs the two promotion
                 // warps that share a scheduler with the UMMA-issuing warp starve it (measured: the UMMA
                 // rate halves).
-                uint32_t v[32];
+                // Eight 16-column chunks (16, not 32: sixteen fewer live registers keep this loop, which sits at
+                // the register limit, free of spills - a few spilled values here cost more than 50 %).
+                uint32_t v[16];
                 if (warp_live) {
-                    ptx::tmem_ld_x32_sync(ta, v);
-                    fold32(acc, v, s0v);
-                    ptx::tmem_ld_x32_sync(ta + 32, v);
-                    fold32(acc + 16, v, s0v);
-                    ptx::tmem_ld_x32_sync(ta + 128, v);
-                    fold32(acc + 32, v, s1v);
-                    ptx::tmem_ld_x32_sync(ta + 160, v);
+#pragma unroll
+                    for (int c = 0; c < 7; ++c) {
+                        ptx::tmem_ld_x16_sync(ta + (c >> 2) * 128 + (c & 3) * 16, v);
+                        fold16(acc + 8 * c, v, (c < 4) ? s0v : s1v);
+                    }
+                    ptx::tmem_ld_x16_sync(ta + 128 + 48, v);
                 }
                 // all reads of this TMEM stage are done: hand it back to the MMA warp
                 ptx::tc_fence_before();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(tempty_bar(ts));
-                if (warp_live) fold32(acc + 48, v, s1v);
+                if (warp_live) fold16(acc + 56, v, s1v);
             }
             if (!ok) break;
 
