@@ -88,7 +88,6 @@ struct GemmParams {
     float* acc;              // stage 2 out [M, H] fp32
     int* status;
     int use_weight;          // multiply this stage's GEMM result by the route weight (sorted_w)
-    int act;                 // stage 1 activation: 0 = SiLU, 1 = GELU (erf form)
 };
 
 // torch: silu(x) = x / (1 + exp(-x)) in fp32, then * up (aiter/fused_moe.py:3676).
@@ -106,7 +105,8 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
 __device__ __forceinline__ float gelu_mul(float g, float u) {
     return 0.5f * g * (1.0f + erff(g * 0.70710678118654752440f)) * u;
 }
-__device__ __forceinline__ float act_mul(int act, float g, float u) { return act == 1 ? gelu_mul(g, u) : silu_mul(g, u); }
+template <int ACT>
+__device__ __forceinline__ float act_mul(float g, float u) { return ACT == 1 ? gelu_mul(g, u) : silu_mul(g, u); }
 
 // Correctly rounded a / b given rb = RN(1/b): two FMA residual corrections (the first makes the
 // quotient faithful, the second then rounds it correctly), valid while nothing over- or underflows.
@@ -127,7 +127,9 @@ __device__ __forceinline__ void fold16(float2* acc, const uint32_t* v, float2 s)
 // PT = true : one scale per activation row and one per weight output channel (QuantType.per_Token); the
 //             row scale rides on every K step, the channel scales are applied once in the epilogue, and
 //             stage 1 writes bf16 (the row-wise requantisation needs the whole row and is a kernel of its own).
-template <int STAGE, bool PT>
+// ACT (stage 1 only): 0 = SiLU, 1 = GELU. A compile-time choice: with both bodies in one kernel the 64-fold
+//             unrolled epilogue doubles in size and the SiLU path measurably slows down.
+template <int STAGE, bool PT, int ACT>
 __global__ void __launch_bounds__(kThreads, 1)
 moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -345,7 +347,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                 if (!(ok = ptx::mbar_wait<kEpilogueSleepNs>(tfull_bar(ts), tph, abort_flag))) break;
                 ptx::tc_fence_after();
                 const uint32_t slot = it % kScaleSlots;
-                const float sa = p.use_weight ? scale_a[slot * BM + r] * wgt : scale_a[slot * BM + r];
+                const float sa = scale_a[slot * BM + r] * wgt;   // wgt is exactly 1 when the stage does not weight
                 const float s0 = PT ? sa : sa * scale_w[slot * 2], s1 = PT ? sa : sa * scale_w[slot * 2 + 1];
                 const float2 s0v = make_float2(s0, s0), s1v = make_float2(s1, s1);
                 const uint32_t ta = lane_addr + ts * BN + half * 64;
@@ -395,7 +397,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                 uint32_t w[32];
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {
-                    __nv_bfloat162 h = __floats2bfloat162_rn(act_mul(p.act, acc[j].x, acc[32 + j].x), act_mul(p.act, acc[j].y, acc[32 + j].y));
+                    __nv_bfloat162 h = __floats2bfloat162_rn(act_mul<ACT>(acc[j].x, acc[32 + j].x), act_mul<ACT>(acc[j].y, acc[32 + j].y));
                     w[j] = *reinterpret_cast<uint32_t*>(&h);
                 }
                 uint4* dst = reinterpret_cast<uint4*>(p.a2 + ((size_t)prow * p.inter + nt * 128 + half * 64) * 2);
@@ -407,8 +409,8 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                 float amax = 0.f;
 #pragma unroll
                 for (int j = 0; j < 32; ++j) {   // acc[j] is overwritten by the two activations it feeds
-                    float h0 = __bfloat162float(__float2bfloat16_rn(act_mul(p.act, acc[j].x, acc[32 + j].x)));
-                    float h1 = __bfloat162float(__float2bfloat16_rn(act_mul(p.act, acc[j].y, acc[32 + j].y)));
+                    float h0 = __bfloat162float(__float2bfloat16_rn(act_mul<ACT>(acc[j].x, acc[32 + j].x)));
+                    float h1 = __bfloat162float(__float2bfloat16_rn(act_mul<ACT>(acc[j].y, acc[32 + j].y)));
                     acc[j] = make_float2(h0, h1);
                     amax = fmaxf(amax, fmaxf(fabsf(h0), fabsf(h1)));
                 }
@@ -533,19 +535,19 @@ CUtensorMap make_weight_map(const void* ptr, uint64_t rows, uint64_t K) {
     return m;
 }
 
-template <int STAGE, bool PT>
+template <int STAGE, bool PT, int ACT = 0>
 void launch_gemm(const CUtensorMap& tmap, const GemmParams& p, int64_t max_tiles, int dev, cudaStream_t stream,
                  int sm_margin = 0) {
     static bool attr_set[64] = {false};
     if (dev >= 64 || !attr_set[dev]) {
-        B200_CUDA(cudaFuncSetAttribute(moe_gemm_kernel<STAGE, PT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        B200_CUDA(cudaFuncSetAttribute(moe_gemm_kernel<STAGE, PT, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        kSmemBytes));
         if (dev < 64) attr_set[dev] = true;
     }
     int64_t grid = sm_count(dev) - sm_margin;   // SMs left free for a collective running beside this kernel
     if (max_tiles < grid) grid = max_tiles;
     if (grid < 1) return;
-    moe_gemm_kernel<STAGE, PT><<<(unsigned)grid, kThreads, kSmemBytes, stream>>>(tmap, p);
+    moe_gemm_kernel<STAGE, PT, ACT><<<(unsigned)grid, kThreads, kSmemBytes, stream>>>(tmap, p);
     B200_CUDA(cudaGetLastError());
 }
 
@@ -618,11 +620,12 @@ void launch_moe_stage1(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale,
     p.status = (int*)status->ptr;
     p.sorted_w = sorted_w ? (const float*)sorted_w->ptr : nullptr;
     p.use_weight = sorted_w != nullptr;   // doweight_stage1 (aiter/fused_moe.py:3651-3652)
-    p.act = activation;
     CUtensorMap tmap = make_weight_map(w1->ptr, (uint64_t)(E * N2), (uint64_t)H);
     const int64_t max_tiles = ((int64_t)sorted_ids->numel_ / BM) * p.n_tiles;
-    if (pt) launch_gemm<1, true>(tmap, p, max_tiles, a1->device_id, stream);
-    else launch_gemm<1, false>(tmap, p, max_tiles, a1->device_id, stream);
+    if (pt && activation == 1) launch_gemm<1, true, 1>(tmap, p, max_tiles, a1->device_id, stream);
+    else if (pt) launch_gemm<1, true, 0>(tmap, p, max_tiles, a1->device_id, stream);
+    else if (activation == 1) launch_gemm<1, false, 1>(tmap, p, max_tiles, a1->device_id, stream);
+    else launch_gemm<1, false, 0>(tmap, p, max_tiles, a1->device_id, stream);
 }
 
 void launch_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* a2_scale, const aiter_tensor_t* w2,
