@@ -38,7 +38,7 @@ namespace {
 constexpr int BM = 128;            // sorted rows per tile (== sort unit)
 constexpr int BK = 128;            // K elements (bytes) per pipeline step == scale block
 constexpr int BN = 256;            // UMMA N: 128 gate + 128 up columns, or 256 output columns
-constexpr int kStages = 4;         // shared-memory pipeline depth
+constexpr int kStages = 3;         // shared-memory pipeline depth (4 measured no faster; the space stages stage 2's output)
 constexpr int kABytes = BM * BK;   // 16 KB
 constexpr int kBBytes = BN * BK;   // 32 KB
 constexpr int kThreads = 512;
@@ -63,9 +63,9 @@ constexpr int kScaleSlots = 8;                              // ring of per-K-blo
 constexpr int kOffScaleA = kOffAmax + 2 * 2 * BM * 4;       // float [kScaleSlots][128 rows]
 constexpr int kOffScaleW = kOffScaleA + kScaleSlots * BM * 4;  // float [kScaleSlots][2]
 constexpr int kOffRowTab = kOffScaleW + kScaleSlots * 2 * 4;   // uint32 [2 tiles][128 rows]
-constexpr int kStageRow = 20;                                  // floats per staged row: 16 + 4 of padding
-constexpr int kOffStage = kOffRowTab + 2 * BM * 4;             // float [8 warps][32 rows][kStageRow] (stage 2)
-constexpr int kSmemUsed = kOffStage + 8 * 32 * kStageRow * 4;
+constexpr int kStageRowBytes = 272;                            // staged output row: 64 floats + 16 B (bank spread)
+constexpr int kOffStage = (kOffRowTab + 2 * BM * 4 + 15) & ~15;   // [8 warps][32 rows][kStageRowBytes] (stage 2)
+constexpr int kSmemUsed = kOffStage + 8 * 32 * kStageRowBytes;
 constexpr int kSmemBytes = kSmemUsed + 1024;                // slack for the 1024-byte alignment
 
 struct GemmParams {
@@ -488,42 +488,36 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                 for (int j = 0; j < 4; ++j) dst[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
                 if (half == 0) p.a2_scale[(size_t)prow * (p.inter / 128) + nt] = scale;
             } else {
-                // out[token] += weight * row  (aiter/fused_moe.py:3802-3811) as fp32 L2 reductions; the
+                // out[token] += weight * row  (aiter/fused_moe.py:3802-3811) as fp32 reductions in L2; the
                 // weight is already in the accumulators (it rode on the per-step scales).
-                // A thread holds one row, so reductions issued straight from registers would hit 32
-                // different rows per instruction (16 B each).  Each warp instead passes 16-column
-                // chunks through a padded shared-memory buffer and re-reads them with 4 lanes per row:
-                // one instruction then covers 8 rows x 64 contiguous bytes.
-                const int my_tok = valid ? tok : -1;
-                const int H = p.n_rows;
-                float* sbuf = reinterpret_cast<float*>(smem + kOffStage) + (warp - kEpiWarp0) * (32 * kStageRow);
-                const bool warp_valid = __any_sync(0xffffffffu, valid);
-                const int n_chunks = (nt * 256 + 128 < H) ? 8 : 4;
-                if (warp_valid) {
+                // A thread holds one row. It writes 64 columns (256 contiguous bytes of the output row) to its own
+                // shared-memory row and hands them to the copy engine as ONE asynchronous bulk reduce-add, then the
+                // other 64 once the engine has read the first out (the buffer holds half a tile).
+                // Measured: an SM gets ~20 B/clock of fp32 reductions into L2 whether they are issued as
+                // red.global.v4 from registers or as bulk reductions (plain stores: ~35 B/clock), i.e. ~6k clocks
+                // per tile that the MMA warp, at most two K steps ahead, waits out; hiding them needs a buffer
+                // for the whole 128 KB tile, which neither shared nor tensor memory has room for.
+                const uint32_t srow = sbase + kOffStage + (uint32_t)((warp - kEpiWarp0) * 32 + lane) * kStageRowBytes;
+                const int n_groups = (nt * 256 + 128 < p.n_rows) ? 2 : 1;
+                if (valid) {
+                    float* orow = p.acc + (size_t)tok * p.acc_ld + (nt - p.nt0) * 256 + half * 64;
 #pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        if (c < n_chunks) {
-                            const int a0 = (c < 4) ? c * 8 : 32 + (c - 4) * 8;   // first float2 of the chunk
-                            const int col0 = nt * 256 + ((c < 4) ? 0 : 128) + half * 64 + (c & 3) * 16;
-                            float4* wr = reinterpret_cast<float4*>(sbuf + lane * kStageRow);
+                    for (int g = 0; g < 2; ++g) {
+                        if (g < n_groups) {
+                            ptx::bulk_wait_read_all();   // the copy engine has read this row's previous contents
 #pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                                wr[j] = make_float4(acc[a0 + 2 * j].x, acc[a0 + 2 * j].y,
-                                                    acc[a0 + 2 * j + 1].x, acc[a0 + 2 * j + 1].y);
-                            __syncwarp();
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const int idx = i * 32 + lane, rr = idx >> 2, c4 = idx & 3;
-                                const float4 v = *reinterpret_cast<const float4*>(sbuf + rr * kStageRow + c4 * 4);
-                                const int tk = __shfl_sync(0xffffffffu, my_tok, rr);
-                                if (tk >= 0) ptx::red_add_v4(p.acc + (size_t)tk * p.acc_ld + (col0 - p.nt0 * 256) + c4 * 4, v.x, v.y, v.z, v.w);
-                            }
-                            __syncwarp();
+                            for (int j = 0; j < 16; ++j)
+                                ptx::st_shared_v4(srow + j * 16, acc[g * 32 + 2 * j].x, acc[g * 32 + 2 * j].y,
+                                                  acc[g * 32 + 2 * j + 1].x, acc[g * 32 + 2 * j + 1].y);
+                            ptx::fence_proxy_async();
+                            ptx::bulk_reduce_add_f32(orow + g * 128, srow, 256);
+                            ptx::bulk_commit();
                         }
                     }
                 }
             }
         }
+        ptx::bulk_wait_all();   // nothing of this thread is in flight when the CTA winds down
     }
 
     // ------------------------------------------------------------------------ tail
@@ -696,6 +690,7 @@ void launch_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* a2_scale,
                    (col_end % 256 == 0 || col_end == H),
                "column range [", col_begin, ", ", col_end, ") must lie in [0, model_dim] on 256-column boundaries");
     B200_CHECK(acc->shape[1] == col_end - col_begin, "acc must be [M, col_end - col_begin]");
+    B200_CHECK(((uintptr_t)acc->ptr & 15) == 0, "acc must be 16-byte aligned (bulk reductions)");
     B200_CHECK(sm_margin >= 0 && sm_margin < 128, "sm_margin must be in [0, 128)");
     B200_CHECK(I % 128 == 0 && H % 128 == 0, "inter_dim and model_dim must be multiples of 128");
     if (pt) {
