@@ -239,6 +239,34 @@ def kernel_breakdown(fm, dev_args, reps=5):
     return {k: sum(v) / len(v) for k, v in acc.items()}
 
 
+def library_fp8_gemm_tflops(dev, n=8192, iters=20):
+    """Throughput of the vendor library's dense e4m3 GEMM (n^3, tensor-wise scales, bf16 out), event-timed here:
+    the FP8 tensor-core rate a library kernel reaches on this GPU in this run, reported beside the roofline
+    denominator. None if the call is unavailable."""
+    try:
+        a = torch.randn((n, n), device=dev).to(torch.float8_e4m3fn)
+        b = torch.randn((n, n), device=dev).to(torch.float8_e4m3fn)
+        one = torch.ones((), device=dev, dtype=torch.float32)
+
+        def f():
+            return torch._scaled_mm(a, b.t(), scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+
+        for _ in range(5):
+            f()
+        torch.cuda.synchronize(dev)
+        ts = []
+        for _ in range(iters):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            f()
+            e1.record()
+            e1.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return 2.0 * n ** 3 / (statistics.median(ts) * 1e-3) / 1e12
+    except Exception:   # noqa: BLE001 - a missing or changed private API must not break the bench
+        return None
+
+
 def emit(line):
     """The one JSON line goes to the real stdout; everything else this process (or a library such as NCCL,
     which prints a version banner) writes to stdout has been pointed at stderr."""
@@ -368,6 +396,10 @@ def main():
                                            "the driver's peak file has no FP8 entry",
                             "stage2_achieved": s2, "stage2_frac": s2 / fp8_peak}
         line["layer_frac_of_fp8_peak"] = value / fp8_peak
+        lib = library_fp8_gemm_tflops(dev)
+        if lib is not None:
+            line["roofline"]["library_fp8_gemm_tflops"] = lib
+            line["roofline"]["frac_of_library_fp8_gemm"] = s1 / lib
     if world == 1 and not args.skip_decode:
         # ---- decode case (M=64): HBM-bound weight streaming
         xd, twd, tid = make_tokens(M_DECODE, seed=1)
