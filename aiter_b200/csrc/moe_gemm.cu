@@ -13,12 +13,13 @@
 // Per tile and per 128-wide K block:
 //   warp 0      TMA-loads two [128 rows x 128 B] weight boxes (gate+up rows, or 256 output rows)
 //               into a 128B-swizzled shared-memory stage;
-//   warps 4-7   gather the 128 activation rows of the block (cp.async, 16 B chunks, same swizzle)
-//               and the K block's scales; completion is signalled by cp.async.mbarrier.arrive;
+//   warps 4-7   gather the 128 activation rows of the block (cp.async, 16 B chunks, same swizzle);
+//               completion is signalled by cp.async.mbarrier.arrive;
 //   warp 1      issues 4 tcgen05.mma (M128 N256 K32, e4m3 -> fp32) into one of two 256-column
 //               TMEM stages, then commits to free the smem stage and to publish the TMEM stage;
 //   warps 8-15  read the TMEM stage (tcgen05.ld) and fold it into fp32 registers with the block
-//               scales:  acc += partial * (a_scale[row, kb] * w_scale[e, nblk, kb]).
+//               scales:  acc += partial * (a_scale[row, kb] * w_scale[e, nblk, kb])  (the scales are read
+//               from global memory one K block ahead).
 // The scales are fp32 per 128-K block (not UE8M0 per 32), so the hardware block-scaled MMA kinds do
 // not apply; the per-K-block promotion runs on the CUDA cores and overlaps the next block's MMAs.
 // After the last K block the same warps run the stage's epilogue from registers.
@@ -59,10 +60,7 @@ constexpr int kNumBars = 2 * kStages + 4;
 constexpr int kOffTmemSlot = kOffBar + kNumBars * 8;
 constexpr int kOffAbort = kOffTmemSlot + 4;
 constexpr int kOffAmax = (kOffAbort + 4 + 15) & ~15;        // float [2 tiles][2 halves][128 rows]
-constexpr int kScaleSlots = 8;                              // ring of per-K-block scales (> kStages + 2)
-constexpr int kOffScaleA = kOffAmax + 2 * 2 * BM * 4;       // float [kScaleSlots][128 rows]
-constexpr int kOffScaleW = kOffScaleA + kScaleSlots * BM * 4;  // float [kScaleSlots][2]
-constexpr int kOffRowTab = kOffScaleW + kScaleSlots * 2 * 4;   // uint32 [2 tiles][128 rows]
+constexpr int kOffRowTab = kOffAmax + 2 * 2 * BM * 4;       // uint32 [2 tiles][128 rows]
 constexpr int kStageRowBytes = 272;                            // staged output row: 64 floats + 16 B (bank spread)
 constexpr int kOffStage = (kOffRowTab + 2 * BM * 4 + 15) & ~15;   // [8 warps][32 rows][kStageRowBytes] (stage 2)
 constexpr int kSmemUsed = kOffStage + 8 * 32 * kStageRowBytes;
@@ -165,8 +163,6 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kOffTmemSlot);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffAbort);
     float* amax_x = reinterpret_cast<float*>(smem + kOffAmax);
-    const volatile float* scale_a = reinterpret_cast<const volatile float*>(smem + kOffScaleA);
-    const volatile float* scale_w = reinterpret_cast<const volatile float*>(smem + kOffScaleW);
 
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
     const int lane = threadIdx.x & 31;
@@ -281,40 +277,31 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
             } else {
                 my_row = (uint32_t)prow;
             }
-            const bool my_valid = my_row != 0xFFFFFFFFu;
-            const float* as_src = p.a_scale + (size_t)(my_valid ? my_row : 0u) * (PT ? 1 : p.KB);
             row_tab[tile_par * BM + r] = my_row;
             ptx::named_barrier(2, BM);       // the 128 gather threads; table of the previous tile is
                                              // untouched (other parity), so one barrier per tile suffices
-            const uint8_t* src[8];
-            uint32_t nbytes[8], dst_off[8];
+            // source of pass i in 16-byte units from p.a (32 bits cover 64 GB), validity as a bit mask, and the
+            // two swizzled destination offsets (even / odd pass): few registers, this role runs with 56
+            uint32_t src16[8], vmask = 0;
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const int row = gw * 32 + i * 4 + sub;
-                const uint32_t sr = row_tab[tile_par * BM + row];
-                nbytes[i] = sr != 0xFFFFFFFFu ? 16u : 0u;   // pads: zero-filled rows
-                src[i] = p.a + (size_t)(nbytes[i] ? sr : 0u) * p.K + chunk * 16;
-                dst_off[i] = (uint32_t)row * BK + ((chunk ^ (uint32_t)(row & 7)) << 4);
+                const uint32_t sr = row_tab[tile_par * BM + gw * 32 + i * 4 + sub];
+                const bool live = sr != 0xFFFFFFFFu;   // pads: zero-filled rows
+                vmask |= (live ? 1u : 0u) << i;
+                src16[i] = (live ? sr : 0u) * (uint32_t)(p.K >> 4) + chunk;
             }
-            // threads 0 and 1 also fetch the two weight-block scales of this tile
-            const float* ws_src = p.w_scale;
-            if (!PT && r < 2) {
-                const int e = p.sorted_eids[blk];
-                int nb;
-                if (STAGE == 1) nb = (r == 0) ? nt : p.inter / 128 + nt;
-                else nb = (r == 0) ? nt * 2 : min(nt * 2 + 1, p.n_rows / 128 - 1);
-                ws_src = p.w_scale + ((size_t)e * (p.n_rows / 128) + nb) * p.KB;
-            }
+            const uint32_t row0 = (uint32_t)(gw * 32 + sub);   // row of pass i: row0 + 4 i, so (row & 7) = sub or 4 + sub
+            const uint32_t d_even = row0 * BK + ((chunk ^ (uint32_t)sub) << 4);
+            const uint32_t d_odd = row0 * BK + ((chunk ^ (uint32_t)(4 + sub)) << 4);
             for (int kb = 0; kb < p.KB; ++kb, ++it) {
                 const int s = it % kStages;
                 const uint32_t ph = (it / kStages) & 1u;
                 if (!(ok = ptx::mbar_wait<kProducerSleepNs>(empty_bar(s), ph ^ 1u, abort_flag))) break;
                 const uint32_t dst = sA + s * kABytes;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) ptx::cp_async16(dst + dst_off[i], src[i] + (size_t)kb * BK, nbytes[i]);
-                const uint32_t slot = it % kScaleSlots;
-                ptx::cp_async4(sbase + kOffScaleA + (slot * BM + r) * 4, as_src + (PT ? 0 : kb), my_valid ? 4u : 0u);
-                if (!PT && r < 2) ptx::cp_async4(sbase + kOffScaleW + (slot * 2 + r) * 4, ws_src + kb, 4u);
+                for (int i = 0; i < 8; ++i)
+                    ptx::cp_async16(dst + ((i & 1) ? d_odd : d_even) + i * 4 * BK, p.a + ((size_t)src16[i] << 4) + (size_t)kb * BK,
+                                    ((vmask >> i) & 1u) ? 16u : 0u);
                 // the arrival is delivered by the copy engine when this thread's copies have landed,
                 // so the thread can go on to the next stage at once (all kStages stay in flight)
                 ptx::cp_async_mbar_arrive(full_bar(s));
@@ -334,23 +321,25 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
         bool ok = true;
         // row info of the next tile is fetched one tile ahead, so its latency is off the path between
         // two tiles (where the MMA warp can only run two K steps ahead of these warps)
-        int tok_next = 0;
+        int tok_next = 0, eid_next = 0;
         float wgt_next = 0.f;
         if ((int)blockIdx.x < total_tiles) {
             const int prow0 = ((int)blockIdx.x / p.n_tiles) * BM + r;
             tok_next = p.sorted_ids[prow0] & 0xFFFFFF;
+            eid_next = p.sorted_eids[(int)blockIdx.x / p.n_tiles];
             if (p.use_weight) wgt_next = p.sorted_w[prow0];
         }
         for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, tile_par ^= 1u) {
             const int blk = t / p.n_tiles, nt = t - blk * p.n_tiles + p.nt0;
             const int prow = blk * BM + r;
-            const int tok = tok_next;
+            const int tok = tok_next, eid = eid_next;
             const bool valid = tok < tokens;
             // the route weight (stage 2, or stage 1 with doweight_stage1) rides on the per-step scales
             const float wgt = p.use_weight ? (valid ? wgt_next : 0.f) : 1.f;
             if (t + (int)gridDim.x < total_tiles) {
                 const int prow1 = ((t + (int)gridDim.x) / p.n_tiles) * BM + r;
                 tok_next = p.sorted_ids[prow1] & 0xFFFFFF;
+                eid_next = p.sorted_eids[(t + (int)gridDim.x) / p.n_tiles];
                 if (p.use_weight) wgt_next = p.sorted_w[prow1];
             }
             // a warp whose 32 rows are all padding (decode: most of them) leaves its accumulators at 0
@@ -362,14 +351,32 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
 #pragma unroll
             for (int j = 0; j < 64; ++j) acc[j] = make_float2(0.f, 0.f);
 
+            // Per-step scales come straight from global memory (L1/L2), fetched one K step ahead: a load from
+            // shared memory issued after the UMMA's completion sits ~150 clocks (shared memory is saturated by
+            // operand reads and fills) on the path to the first FMA.
+            // (32-bit element offsets from the parameter pointers: two registers fewer than pointers)
+            const uint32_t a_so = (uint32_t)(valid ? (STAGE == 1 ? tok : prow) : 0) * (uint32_t)(PT ? 1 : p.KB);
+            uint32_t w_so = 0, w_so1 = 0;
+            if (!PT) {
+                const int nb0 = (STAGE == 1) ? nt : nt * 2;
+                const int nb1 = (STAGE == 1) ? p.inter / 128 + nt : min(nt * 2 + 1, p.n_rows / 128 - 1);
+                w_so = (uint32_t)((eid * (p.n_rows / 128) + nb0) * p.KB);
+                w_so1 = w_so + (uint32_t)((nb1 - nb0) * p.KB);
+            }
+            float pf_a = __ldg(p.a_scale + a_so), pf_w0 = PT ? 1.f : __ldg(p.w_scale + w_so), pf_w1 = PT ? 1.f : __ldg(p.w_scale + w_so1);
+
             for (int kb = 0; kb < p.KB; ++kb, ++it) {
                 const int ts = it & 1;
                 const uint32_t tph = (it >> 1) & 1u;
                 if (!(ok = ptx::mbar_wait<kEpilogueSleepNs>(tfull_bar(ts), tph, abort_flag))) break;
                 ptx::tc_fence_after();
-                const uint32_t slot = it % kScaleSlots;
-                const float sa = scale_a[slot * BM + r] * wgt;   // wgt is exactly 1 when the stage does not weight
-                const float s0 = PT ? sa : sa * scale_w[slot * 2], s1 = PT ? sa : sa * scale_w[slot * 2 + 1];
+                const float sa = pf_a * wgt;   // wgt is exactly 1 when the stage does not weight
+                const float s0 = PT ? sa : sa * pf_w0, s1 = PT ? sa : sa * pf_w1;
+                if (!PT && kb + 1 < p.KB) {
+                    pf_a = __ldg(p.a_scale + a_so + kb + 1);
+                    pf_w0 = __ldg(p.w_scale + w_so + kb + 1);
+                    pf_w1 = __ldg(p.w_scale + w_so1 + kb + 1);
+                }
                 const float2 s0v = make_float2(s0, s0), s1v = make_float2(s1, s1);
                 const uint32_t ta = lane_addr + ts * BN + half * 64;
                 // load + wait, then packed FMAs.  The packed fp32x2 FMAs matter:
