@@ -224,15 +224,21 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
             }
         } else if (warp == 1 && lane == 0) {
             // ---------------------------------------------------------------- UMMA issuer
-            uint32_t it = 0;
+            // Block scales (PT = false): every K block's partial sums go to the TMEM stage of that step's parity
+            // and are promoted in registers. Row/channel scales (PT = true) do not depend on K: the whole K loop
+            // accumulates in one TMEM stage, stages alternate per TILE, and the epilogue of a tile overlaps the
+            // MMAs of the next.
+            uint32_t it = 0, tile_it = 0;
             bool ok = true;
-            for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+            for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++tile_it) {
                 for (int kb = 0; kb < p.KB; ++kb, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1u;
-                    const int ts = it & 1;
-                    const uint32_t tph = (it >> 1) & 1u;
-                    if (!(ok = ptx::mbar_wait(tempty_bar(ts), tph ^ 1u, abort_flag))) break;
+                    const uint32_t tcount = PT ? tile_it : it;   // what the TMEM stage ring counts
+                    const int ts = tcount & 1;
+                    const uint32_t tph = (tcount >> 1) & 1u;
+                    if (!PT || kb == 0)
+                        if (!(ok = ptx::mbar_wait(tempty_bar(ts), tph ^ 1u, abort_flag))) break;
                     if (!(ok = ptx::mbar_wait(full_bar(s), ph, abort_flag))) break;
                     // the activation rows were written by cp.async (generic proxy); order them
                     // before the tensor core's async-proxy reads
@@ -243,9 +249,9 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                     const uint32_t d = tmem_base + ts * BN;
 #pragma unroll
                     for (int k = 0; k < BK / 32; ++k)   // 32 bytes of K per UMMA: +2 in 16-byte units
-                        ptx::umma_f8(d, da + 2u * k, db + 2u * k, kIdesc, k > 0 ? 1u : 0u);
+                        ptx::umma_f8(d, da + 2u * k, db + 2u * k, kIdesc, (k > 0 || (PT && kb > 0)) ? 1u : 0u);
                     ptx::umma_commit(empty_bar(s));
-                    ptx::umma_commit(tfull_bar(ts));
+                    if (!PT || kb == p.KB - 1) ptx::umma_commit(tfull_bar(ts));
                 }
             }
         }
@@ -365,7 +371,8 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
             }
             float pf_a = __ldg(p.a_scale + a_so), pf_w0 = PT ? 1.f : __ldg(p.w_scale + w_so), pf_w1 = PT ? 1.f : __ldg(p.w_scale + w_so1);
 
-            for (int kb = 0; kb < p.KB; ++kb, ++it) {
+            // PT: one pass over the finished accumulators per tile (it counts tiles), else one per K block
+            for (int kb = PT ? p.KB - 1 : 0; kb < p.KB; ++kb, ++it) {
                 const int ts = it & 1;
                 const uint32_t tph = (it >> 1) & 1u;
                 if (!(ok = ptx::mbar_wait<kEpilogueSleepNs>(tfull_bar(ts), tph, abort_flag))) break;
