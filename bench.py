@@ -389,9 +389,9 @@ def main():
         s2 = 2.0 * M_PREFILL * TOPK * H * I / (kb["stage2"] * 1e-3) / 1e12
         line["roofline"] = {"bound": "tensor", "kernel": "moe_gemm_kernel<1> (stage 1)", "achieved": s1,
                             "peak": fp8_peak, "unit": "TFLOP/s", "frac": s1 / fp8_peak,
-                            # DRAM bytes of one stage-1 launch: ncu capture of the M=1024, E=32 case (1.169 GB)
+                            # DRAM bytes of one stage-1 launch: ncu capture of the M=1024, E=32 case (1.172 GB)
                             # scaled by the expert count (profiles/moe_gemm_kernel_small_case_M1024_E32_full.md)
-                            "traffic": 1.169e9 * E / 32 if M_PREFILL == 8192 else None,
+                            "traffic": 1.172e9 * E / 32 if M_PREFILL == 8192 else None,
                             "peak_source": f"2 x bf16_tflops of {pk['source']} ({pk['bf16_tflops']} TFLOP/s burst); "
                                            "the driver's peak file has no FP8 entry",
                             "stage2_achieved": s2, "stage2_frac": s2 / fp8_peak}
