@@ -371,6 +371,8 @@ def fused_moe(
         raise ValueError("fused_moe: topk_weight must be float32")
     if topk_ids.dtype != dtypes.i32:
         raise ValueError("fused_moe: topk_ids must be int32")
+    if M == 0:   # nothing to compute: the reference allocates the same empty result (aiter/fused_moe.py:579-619)
+        return torch.empty((0, model_dim), dtype=dtype, device=hidden_states.device)
     return fused_moe_stages(hidden_states, w1.contiguous(), w2.contiguous(), topk_weight, topk_ids,
                             expert_mask, w1_scale.contiguous(), w2_scale.contiguous(), a1_scale,
                             num_local_tokens, dtype, quant_type=quant_type, activation=activation,

@@ -155,6 +155,29 @@ def test_shapes_against_oracle(M, H, I, E, topk, routing):
     assert_parity(run(c), ref, f"{M}x{H}x{I} E{E} top{topk}")
 
 
+def test_empty_batch():
+    c = to_dev(inputs.make_config("cfg0", seed=0))
+    out = aiter_b200.fused_moe(c["x"][:0], c["w1_q"], c["w2_q"], c["topk_weight"][:0], c["topk_ids"][:0],
+                               quant_type=QT.per_1x128, w1_scale=c["w1_scale"], w2_scale=c["w2_scale"])
+    assert out.shape == (0, c["x"].shape[1]) and out.dtype == torch.bfloat16
+
+
+@pytest.mark.parametrize("M", [128, 129, 300])
+def test_every_route_to_one_expert(M):
+    """Maximum collision: all tokens pick the same expert (the others get no block at all); M = 128 and 129 sit on
+    the two sides of a row-block boundary."""
+    H, I, E = 512, 256, 4
+    g = torch.Generator().manual_seed(M)
+    x = torch.randn((M, H), generator=g).to(torch.bfloat16)
+    w1_q, w1_s = inputs.make_weights(E, 2 * I, H, seed=M)
+    w2_q, w2_s = inputs.make_weights(E, H, I, seed=M + 1)
+    ti = torch.full((M, 1), 2, dtype=torch.int32)
+    tw = torch.rand((M, 1), generator=g, dtype=torch.float32) + 0.5
+    ref = moe_oracle.fused_moe_ref(x, w1_q, w1_s, w2_q, w2_s, tw, ti)
+    c = to_dev(dict(x=x, w1_q=w1_q, w1_scale=w1_s, w2_q=w2_q, w2_scale=w2_s, topk_weight=tw, topk_ids=ti))
+    assert_parity(run(c), ref, f"one expert, M={M}")
+
+
 def test_dsv3_decode_full_size():
     """cfg1: M=64, H=7168, I=2048, E=256, topk=8 with DeepSeek-V3 grouped routing. The weights are
     drawn on the GPU (11.3 GB); the oracle runs per expert on the host."""

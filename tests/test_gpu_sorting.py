@@ -67,6 +67,13 @@ def test_random_against_oracle(M, E, topk, B):
         check(run_sort(ids, w, E, B, m, n), exp, f"{M}x{E}x{topk}/{B} {tag}")
 
 
+def test_no_tokens():
+    """M = 0: every slot of the padded output is a pad, no block is valid."""
+    ids, w = torch.zeros((0, 2), dtype=torch.int32), torch.zeros((0, 2), dtype=torch.float32)
+    exp = moe_oracle.moe_sorting_ref(ids, w, 8, 128)
+    check(run_sort(ids, w, 8, 128), exp, "no tokens")
+
+
 def test_skewed_routing_and_empty_experts():
     w, ids = inputs.make_routing("zipf", 4096, 128, 8, seed=5)
     exp = moe_oracle.moe_sorting_ref(ids, w, 128, 128)
