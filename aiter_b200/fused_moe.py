@@ -182,6 +182,12 @@ def get_inter_dim(w1_shape, w2_shape):
     return E, model_dim, inter_dim
 
 
+# Opt-in kernel-bench hook (the reference's ``kernel_bench_callable``, aiter/fused_moe.py:79-82): a caller sets a
+# list here and every layer call appends (name, cuda event) marks before each of its kernels and at its end;
+# None in production, so there is no overhead.
+kernel_bench_events = None
+
+
 def _mark(timers, name):
     if timers is not None:
         ev = torch.cuda.Event(enable_timing=True)
@@ -208,6 +214,8 @@ def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, 
     M, topk = topk_ids.shape
     E, model_dim, inter_dim = get_inter_dim(w1.shape, w2.shape)
     global_E = expert_mask.numel() if expert_mask is not None else E
+    if timers is None:
+        timers = kernel_bench_events
 
     _mark(timers, "sort")
     # stage 2 accumulates into its own fp32 buffer, so no zero-filled moe_buf is asked for
