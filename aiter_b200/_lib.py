@@ -50,6 +50,9 @@ _SIGNATURES = {
     "b200_biased_grouped_topk": (ctypes.c_int, [_T] * 4 + [ctypes.c_int] * 3 + [ctypes.c_float, ctypes.c_void_p]),
     "b200_topk_softmax": (ctypes.c_int, [_T] * 4 + [ctypes.c_int, ctypes.c_void_p]),
     "b200_moe_finalize": (ctypes.c_int, [_T] * 2 + [ctypes.c_void_p]),
+    "b200_ep_push_partials": (ctypes.c_int, [_T] * 3 + [ctypes.c_int] * 3 + [ctypes.c_void_p]),
+    "b200_ep_combine": (ctypes.c_int, [_T] * 4 + [ctypes.c_int] * 3 + [ctypes.c_void_p]),
+    "b200_ep_enable_peer_access": (ctypes.c_int, [ctypes.c_int] * 2),
 }
 
 _lib = None
@@ -96,6 +99,15 @@ def to_aiter(t: torch.Tensor | None):
     s.dtype_ = AITER_DTYPE[t.dtype]
     s.device_id = t.device.index if t.is_cuda else -1
     return s
+
+
+def call_plain(name: str, *args):
+    """Calls an int-status entry point that takes plain integers and no stream."""
+    handle = lib()
+    status = getattr(handle, name)(*args)
+    if status != 0:
+        msg = handle.aiter_get_last_error()
+        raise RuntimeError(f"{name} failed: {msg.decode() if msg else 'unknown error'}")
 
 
 def call(name: str, *args, device: torch.device | None = None):

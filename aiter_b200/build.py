@@ -10,7 +10,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libaiter_b200.so")
-SOURCES = ["abi.cu", "moe_sorting.cu", "quant_1x128.cu", "moe_gemm.cu", "moe_routing.cu"]
+SOURCES = ["abi.cu", "moe_sorting.cu", "quant_1x128.cu", "moe_gemm.cu", "moe_routing.cu", "ep_exchange.cu"]
 HEADERS = ["common.cuh", "sm100_ptx.cuh", os.path.join("..", "..", "include", "aiter_b200.h")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",

@@ -33,6 +33,10 @@ void launch_moe_stage2(const aiter_tensor_t*, const aiter_tensor_t*, const aiter
 void launch_biased_grouped_topk(const aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*, int, int,
                                 int, float, cudaStream_t);
 void launch_topk_softmax(aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*, const aiter_tensor_t*, int, cudaStream_t);
+void launch_ep_push(const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, int, int, int, cudaStream_t);
+void launch_ep_combine(aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, int, int, int,
+                       cudaStream_t);
+void enable_peer_access(int, int);
 
 namespace {
 
@@ -203,6 +207,30 @@ B200_EXPORT int b200_moe_finalize(aiter_tensor_t* out, const aiter_tensor_t* acc
         DeviceGuard g(acc->device_id);
         launch_finalize(out, acc, (cudaStream_t)stream);
     });
+}
+
+B200_EXPORT int b200_ep_push_partials(const aiter_tensor_t* acc, const aiter_tensor_t* topk_ids,
+                                      const aiter_tensor_t* peer_recv, int rank, int world, int experts_per_rank,
+                                      void* stream) {
+    return safe_call([&] {
+        B200_CHECK(acc != nullptr, "acc must not be NULL");
+        DeviceGuard g(acc->device_id);
+        launch_ep_push(acc, topk_ids, peer_recv, rank, world, experts_per_rank, (cudaStream_t)stream);
+    });
+}
+
+B200_EXPORT int b200_ep_combine(aiter_tensor_t* out, const aiter_tensor_t* acc, const aiter_tensor_t* recv,
+                                const aiter_tensor_t* topk_ids, int rank, int world, int experts_per_rank,
+                                void* stream) {
+    return safe_call([&] {
+        B200_CHECK(acc != nullptr, "acc must not be NULL");
+        DeviceGuard g(acc->device_id);
+        launch_ep_combine(out, acc, recv, topk_ids, rank, world, experts_per_rank, (cudaStream_t)stream);
+    });
+}
+
+B200_EXPORT int b200_ep_enable_peer_access(int device, int peer_device) {
+    return safe_call([&] { enable_peer_access(device, peer_device); });
 }
 
 }  // extern "C"

@@ -1,0 +1,166 @@
+// Expert-parallel combine over NVLink peer memory: every rank pushes the fp32 partial rows it really
+// produced to the rank that owns the token, the owner adds what arrived to its own partial.
+//
+// Takes the place of the dense fp32 reduce-scatter of the [M, H] partials: with group-limited routing a
+// token has routes on at most half of 8 ranks, so half of the rows of a dense exchange are zeros. The
+// reference reaches the same end with MoRI's combine, or with a stage-2 epilogue that scatters to an arena
+// in peer memory (`Stage2ScatterContext`, aiter/fused_moe.py:536-575; oracle
+// op_tests/multigpu_tests/test_dispatch_combine.py:18-72: the sum over ranks equals the single-GPU result).
+//
+// Protocol per layer call (all stream-ordered, no device-side waiting between ranks):
+//   1. push kernel on rank r: for every token t of another owner o that has a route to one of r's experts,
+//      copy acc_r[t, :] into recv_o[r, t - o*m_local, :] with 16-byte peer stores;
+//   2. a collective of the communication library (any all-reduce) as the barrier: a rank passes it only
+//      after every rank's push kernel has completed, i.e. after all peer stores are performed;
+//   3. combine kernel on owner o: out[t] = round(sum over ranks r in ascending order of
+//      (r == o ? acc_o[t] : recv_o[r, t_local]) for the ranks that touched t). A fixed order: the result
+//      does not depend on arrival order.
+// Whether rank r touched token t follows from the routing table alone (ids / experts_per_rank == r), which
+// every rank holds after the all-gather, so no counts or indices are exchanged and rows that were not
+// written are never read (recv needs no zero-fill).
+//
+// Plain peer loads/stores only: no multimem, no cluster launch.
+
+#include <algorithm>
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+constexpr int kEpThreads = 256;
+constexpr int kMaxWorld = 64;
+
+// bit r set: token has a route to an expert of rank r
+__device__ __forceinline__ unsigned long long touch_mask(const int* __restrict__ ids, int topk, int experts_per_rank,
+                                                         int world) {
+    unsigned long long m = 0;
+    for (int k = 0; k < topk; ++k) {
+        const int e = ids[k];
+        if (e >= 0) {
+            const int r = e / experts_per_rank;
+            if (r < world) m |= 1ull << r;
+        }
+    }
+    return m;
+}
+
+__global__ void __launch_bounds__(kEpThreads) ep_push_kernel(const float4* __restrict__ acc, const int* __restrict__ topk_ids,
+                                                             const long long* __restrict__ peer_recv, int M, int H4,
+                                                             int topk, int rank, int world, int experts_per_rank,
+                                                             int m_local) {
+    for (int t = blockIdx.x; t < M; t += gridDim.x) {
+        const int owner = t / m_local;
+        if (owner == rank) continue;
+        const unsigned long long m = touch_mask(topk_ids + (size_t)t * topk, topk, experts_per_rank, world);
+        if (!((m >> rank) & 1ull)) continue;
+        const float4* src = acc + (size_t)t * H4;
+        float4* dst = reinterpret_cast<float4*>(peer_recv[owner]) + ((size_t)rank * m_local + (t - owner * m_local)) * H4;
+        for (int i = threadIdx.x; i < H4; i += kEpThreads) dst[i] = src[i];
+    }
+    __threadfence_system();   // the peer stores are performed before this kernel counts as complete
+}
+
+template <typename T2>
+__device__ __forceinline__ T2 to_pair(float a, float b);
+template <>
+__device__ __forceinline__ __nv_bfloat162 to_pair<__nv_bfloat162>(float a, float b) { return __floats2bfloat162_rn(a, b); }
+template <>
+__device__ __forceinline__ __half2 to_pair<__half2>(float a, float b) { return __floats2half2_rn(a, b); }
+
+template <typename T2>
+__global__ void __launch_bounds__(kEpThreads) ep_combine_kernel(uint2* __restrict__ out, const float4* __restrict__ acc,
+                                                                const float4* __restrict__ recv,
+                                                                const int* __restrict__ topk_ids, int H4, int topk, int rank,
+                                                                int world, int experts_per_rank, int m_local) {
+    for (int tl = blockIdx.x; tl < m_local; tl += gridDim.x) {
+        const int t = rank * m_local + tl;
+        const unsigned long long m = touch_mask(topk_ids + (size_t)t * topk, topk, experts_per_rank, world);
+        for (int i = threadIdx.x; i < H4; i += kEpThreads) {
+            float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int r = 0; r < world; ++r) {
+                if (!((m >> r) & 1ull)) continue;
+                const float4 v = (r == rank) ? acc[(size_t)t * H4 + i] : recv[((size_t)r * m_local + tl) * H4 + i];
+                s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+            }
+            T2 lo = to_pair<T2>(s.x, s.y), hi = to_pair<T2>(s.z, s.w);
+            out[(size_t)tl * H4 + i] = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        }
+    }
+}
+
+void check_common(const aiter_tensor_t* acc, const aiter_tensor_t* topk_ids, int rank, int world, int experts_per_rank,
+                  int64_t& M, int64_t& H, int64_t& topk, int64_t& m_local) {
+    check_tensor(acc, "acc", AITER_DTYPE_fp32, 2);
+    check_tensor(topk_ids, "topk_ids", AITER_DTYPE_i32, 2);
+    M = acc->shape[0];
+    H = acc->shape[1];
+    topk = topk_ids->shape[1];
+    B200_CHECK(topk_ids->shape[0] == M, "topk_ids must have one row per row of acc");
+    B200_CHECK(world >= 1 && world <= kMaxWorld && rank >= 0 && rank < world, "bad rank/world: ", rank, "/", world);
+    B200_CHECK(experts_per_rank >= 1, "experts_per_rank must be positive");
+    B200_CHECK(M % world == 0, "token count ", M, " must be divisible by the world size ", world);
+    B200_CHECK(H % 4 == 0 && ((uintptr_t)acc->ptr & 15) == 0, "rows must be 16-byte multiples and 16-byte aligned");
+    m_local = M / world;
+}
+
+}  // namespace
+
+void launch_ep_push(const aiter_tensor_t* acc, const aiter_tensor_t* topk_ids, const aiter_tensor_t* peer_recv, int rank,
+                    int world, int experts_per_rank, cudaStream_t stream) {
+    int64_t M, H, topk, m_local;
+    check_common(acc, topk_ids, rank, world, experts_per_rank, M, H, topk, m_local);
+    check_tensor(peer_recv, "peer_recv", AITER_DTYPE_i64, 1);
+    B200_CHECK((int64_t)peer_recv->numel_ == world, "peer_recv needs one address per rank");
+    if (M == 0 || world == 1) return;
+    const int grid = (int)std::min<int64_t>(M, (int64_t)sm_count(acc->device_id) * 8);
+    ep_push_kernel<<<grid, kEpThreads, 0, stream>>>((const float4*)acc->ptr, (const int*)topk_ids->ptr,
+                                                   (const long long*)peer_recv->ptr, (int)M, (int)(H / 4), (int)topk, rank,
+                                                   world, experts_per_rank, (int)m_local);
+    B200_CUDA(cudaGetLastError());
+}
+
+void launch_ep_combine(aiter_tensor_t* out, const aiter_tensor_t* acc, const aiter_tensor_t* recv,
+                       const aiter_tensor_t* topk_ids, int rank, int world, int experts_per_rank, cudaStream_t stream) {
+    int64_t M, H, topk, m_local;
+    check_common(acc, topk_ids, rank, world, experts_per_rank, M, H, topk, m_local);
+    check_tensor(out, "out", -1, 2);
+    B200_CHECK(out->dtype_ == AITER_DTYPE_bf16 || out->dtype_ == AITER_DTYPE_fp16, "out must be bf16 or fp16");
+    B200_CHECK(out->shape[0] == m_local && out->shape[1] == H, "out must be [tokens / world, model_dim]");
+    check_tensor(recv, "recv", AITER_DTYPE_fp32, 3);
+    B200_CHECK(recv->shape[0] == world && recv->shape[1] == m_local && recv->shape[2] == H,
+               "recv must be [world, tokens / world, model_dim]");
+    B200_CHECK(((uintptr_t)recv->ptr & 15) == 0 && ((uintptr_t)out->ptr & 7) == 0, "recv/out alignment");
+    if (m_local == 0) return;
+    const int grid = (int)std::min<int64_t>(m_local, (int64_t)sm_count(acc->device_id) * 8);
+    if (out->dtype_ == AITER_DTYPE_bf16)
+        ep_combine_kernel<__nv_bfloat162><<<grid, kEpThreads, 0, stream>>>(
+            (uint2*)out->ptr, (const float4*)acc->ptr, (const float4*)recv->ptr, (const int*)topk_ids->ptr, (int)(H / 4),
+            (int)topk, rank, world, experts_per_rank, (int)m_local);
+    else
+        ep_combine_kernel<__half2><<<grid, kEpThreads, 0, stream>>>(
+            (uint2*)out->ptr, (const float4*)acc->ptr, (const float4*)recv->ptr, (const int*)topk_ids->ptr, (int)(H / 4),
+            (int)topk, rank, world, experts_per_rank, (int)m_local);
+    B200_CUDA(cudaGetLastError());
+}
+
+// Lets kernels running on `device` read and write memory of `peer_device` (a mapping opened from another
+// process's allocation lives on the exporting GPU). Idempotent.
+void enable_peer_access(int device, int peer_device) {
+    if (device == peer_device) return;
+    DeviceGuard guard(device);
+    int can = 0;
+    B200_CUDA(cudaDeviceCanAccessPeer(&can, device, peer_device));
+    B200_CHECK(can == 1, "GPU ", device, " cannot access GPU ", peer_device, " as a peer");
+    cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
+    if (e == cudaErrorPeerAccessAlreadyEnabled) {
+        cudaGetLastError();   // clear the sticky-free error state
+        return;
+    }
+    B200_CUDA(e);
+}
+
+}  // namespace b200

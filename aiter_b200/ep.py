@@ -14,6 +14,11 @@ Reducing in fp32 keeps the result equal to the single-GPU one up to fp32 summati
 reference reaches the same end with an all-to-all dispatch/combine
 (op_tests/multigpu_tests/test_dispatch_combine.py:75-177, oracle run_ref :18-72).
 
+With ``exchange="p2p"`` step 3 is instead a push of the partial rows a rank really produced into the owning
+rank's memory over NVLink (CUDA IPC mappings, plain peer stores), a tiny all-reduce as the barrier, and a
+combine kernel that adds what arrived in a fixed rank order: rows of tokens without a route on the sending
+rank (with DeepSeek-V3's group-limited routing, half of them at 8 ranks) do not travel.
+
 The collectives go through ``torch.distributed`` so the same code runs on gloo/CPU ranks for the
 host-logic tests; ``local_layer`` is injectable for that purpose.
 """
@@ -55,16 +60,71 @@ def _gpu_finalize(acc, dtype):
     return out
 
 
+class PeerExchange:
+    """Receive buffers for the peer-memory combine, one set per (process group, rows per rank, model_dim).
+
+    Every rank allocates recv [world, m_local, H] fp32, exports it through CUDA IPC (the handle that
+    torch.multiprocessing uses to pass CUDA tensors between processes), maps the buffers of all other ranks
+    and keeps their addresses in a device array for the push kernel. Built once, on first use; building it is
+    a collective call (all ranks of the group must reach it)."""
+
+    _cache: dict = {}
+
+    def __init__(self, group, m_local, H, device):
+        from torch.multiprocessing.reductions import reduce_tensor
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        self.recv = torch.empty((world, m_local, H), dtype=torch.float32, device=device)
+        self.flag = torch.zeros(1, dtype=torch.int32, device=device)
+        exported = [None] * world
+        dist.all_gather_object(exported, reduce_tensor(self.recv), group=group)
+        self.peers = []
+        for r in range(world):
+            if r == rank:
+                self.peers.append(self.recv)
+            else:
+                rebuild, args = exported[r]
+                t = rebuild(*args)      # lives on the exporting rank's GPU, mapped into this process
+                _lib.call_plain("b200_ep_enable_peer_access", int(device.index), int(t.device.index))
+                self.peers.append(t)
+        self.ptrs = torch.tensor([t.data_ptr() for t in self.peers], dtype=torch.int64, device=device)
+        dist.barrier(group=group)       # nobody pushes into a buffer that is not mapped everywhere yet
+
+    @classmethod
+    def get(cls, group, m_local, H, device):
+        key = (id(group) if group is not None else 0, m_local, H, device.index)
+        if key not in cls._cache:
+            cls._cache[key] = cls(group, m_local, H, device)
+        return cls._cache[key]
+
+
+def _p2p_combine(partial, ids, num_experts, group, dtype, timers):
+    """partial [M, H] fp32 of this rank -> out [M/G, H]: push, barrier, combine."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    M, H = partial.shape
+    m_local = M // world
+    ex = PeerExchange.get(group, m_local, H, partial.device)
+    epr = num_experts // world
+    _lib.call("b200_ep_push_partials", partial, ids, ex.ptrs, rank, world, epr, device=partial.device)
+    _mark(timers, "ep_barrier")
+    dist.all_reduce(ex.flag, group=group)   # passes only after every rank's push kernel has completed
+    _mark(timers, "ep_combine")
+    out = torch.empty((m_local, H), dtype=dtype, device=partial.device)
+    _lib.call("b200_ep_combine", out, partial, ex.recv, ids, rank, world, epr, device=partial.device)
+    return out
+
+
 def ep_fused_moe(x_local, w1_local, w2_local, topk_weight_local, topk_ids_local, w1_scale_local,
                  w2_scale_local, num_experts, group=None, dtype=torch.bfloat16,
                  quant=_gpu_quant, local_layer=_gpu_local_layer, finalize=_gpu_finalize, timers=None,
-                 overlap_chunks=None, sm_margin=16):
+                 overlap_chunks=None, sm_margin=16, exchange="nccl"):
     """x_local [M/G, H] bf16, routing [M/G, topk] with GLOBAL expert ids -> out [M/G, H].
 
     Every rank must pass the same number of rows. With ``overlap_chunks`` > 1 stage 2 runs in that many
     column ranges and the reduce-scatter of a finished range is issued beside the computation of the next;
     ``sm_margin`` SMs are kept free for NCCL during those launches. Off by default: on 8 B200s four ranges
-    of 59 MB took as long in total as one 235 MB reduce-scatter after the unsplit stage 2 (1.47 vs 1.40 ms)."""
+    of 59 MB took as long in total as one 235 MB reduce-scatter after the unsplit stage 2 (1.47 vs 1.40 ms).
+    ``exchange``: "nccl" = fp32 reduce-scatter of the partials; "p2p" = push of the produced rows into the
+    owner's memory + combine (see the module docstring; the first call builds the IPC mappings)."""
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     m_local, H = x_local.shape
@@ -120,6 +180,13 @@ def ep_fused_moe(x_local, w1_local, w2_local, topk_weight_local, topk_ids_local,
         timers.pop()   # the local layer's own "end" mark: the next mark takes its place
     else:
         partial = local_layer(a1, a1s, w1_local, w2_local, wts, ids, mask, w1_scale_local, w2_scale_local)
+    if exchange == "p2p" and world > 1:
+        _mark(timers, "ep_push")
+        out = _p2p_combine(partial, ids, num_experts, group, dtype, timers)
+        _mark(timers, "end")
+        return out
+    if exchange not in ("nccl", "p2p"):
+        raise ValueError(f"exchange must be 'nccl' or 'p2p', got {exchange!r}")
     _mark(timers, "ep_reduce_scatter")
     if world == 1:
         mine = partial

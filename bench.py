@@ -288,6 +288,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=M_PREFILL, help="override M (profiling a small case)")
     ap.add_argument("--experts", type=int, default=E, help="override E (profiling a small case)")
     ap.add_argument("--skip-decode", action="store_true")
+    ap.add_argument("--ep-exchange", default="nccl", choices=["nccl", "p2p"],
+                    help="N>1: fp32 reduce-scatter of the partial sums, or peer-memory push + combine")
     ap.add_argument("--cuda-profiler-range", action="store_true",
                     help="bracket the device-timed steps with cudaProfilerStart/Stop (ncu --profile-from-start off)")
     args = ap.parse_args()
@@ -339,10 +341,10 @@ def main():
             return aiter_b200.fused_moe(a, w1_q, w2_q, b, c, quant_type=QT.per_1x128, w1_scale=w1_s, w2_scale=w2_s)
     else:
         def step_dev():
-            return ep.ep_fused_moe(dx, w1_q, w2_q, dtw, dti, w1_s, w2_s, E)
+            return ep.ep_fused_moe(dx, w1_q, w2_q, dtw, dti, w1_s, w2_s, E, exchange=args.ep_exchange)
 
         def layer(a, b, c):
-            return ep.ep_fused_moe(a, w1_q, w2_q, b, c, w1_s, w2_s, E)
+            return ep.ep_fused_moe(a, w1_q, w2_q, b, c, w1_s, w2_s, E, exchange=args.ep_exchange)
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -449,7 +451,7 @@ def main():
         accb = {}
         for _ in range(5):
             timers = []
-            ep.ep_fused_moe(dx, w1_q, w2_q, dtw, dti, w1_s, w2_s, E, timers=timers)
+            ep.ep_fused_moe(dx, w1_q, w2_q, dtw, dti, w1_s, w2_s, E, timers=timers, exchange=args.ep_exchange)
             sync()
             for (n0, e0), (_n1, e1) in zip(timers[:-1], timers[1:]):
                 accb.setdefault(n0, []).append(e0.elapsed_time(e1))

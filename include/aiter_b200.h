@@ -159,6 +159,25 @@ int b200_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* a2_scale,
  * the reference's `out.sum(1).to(dtype)` (aiter/fused_moe.py:3811). */
 int b200_moe_finalize(aiter_tensor_t* out, const aiter_tensor_t* acc, void* stream);
 
+/* Expert-parallel combine over NVLink peer memory, in place of a dense fp32 reduce-scatter of the [M,H]
+ * partial sums. The reference's counterparts are MoRI's combine and the stage-2 scatter epilogue into a
+ * peer-memory arena (`Stage2ScatterContext`, aiter/fused_moe.py:536-575; oracle
+ * op_tests/multigpu_tests/test_dispatch_combine.py:18-72).
+ *   b200_ep_push_partials: rank `rank` copies acc[t,:] (fp32 [M,H], M = world * m_local) of every token t owned
+ *     by another rank o for which topk_ids[t,:] (i32 [M,topk], GLOBAL expert ids) names one of its experts
+ *     (id / experts_per_rank == rank) into recv_o[rank, t - o*m_local, :]; peer_recv is an i64 [world] device
+ *     array with the address of every rank's recv buffer (fp32 [world, m_local, H]) as mapped in this process.
+ *   The caller then runs any collective as a barrier, and
+ *   b200_ep_combine: out[tl,:] (bf16/fp16 [m_local,H]) = round(sum over ranks r, ascending, that have a route of
+ *     token t = rank*m_local + tl, of (r == rank ? acc[t,:] : recv[r,tl,:])).
+ *   b200_ep_enable_peer_access: lets kernels on `device` access memory of `peer_device` (idempotent).
+ * No device-side waiting between ranks; rows that were not pushed are never read. */
+int b200_ep_push_partials(const aiter_tensor_t* acc, const aiter_tensor_t* topk_ids, const aiter_tensor_t* peer_recv,
+                          int rank, int world, int experts_per_rank, void* stream);
+int b200_ep_combine(aiter_tensor_t* out, const aiter_tensor_t* acc, const aiter_tensor_t* recv,
+                    const aiter_tensor_t* topk_ids, int rank, int world, int experts_per_rank, void* stream);
+int b200_ep_enable_peer_access(int device, int peer_device);
+
 /* DeepSeek-V3 style router: sigmoid scores, correction bias for the choice only, groups ranked by the sum
  * of their two best biased scores, top `topk_group` groups kept, top-k experts among them; weights are the
  * un-biased scores, renormalised when asked, times routed_scaling_factor. Replaces biased_grouped_topk

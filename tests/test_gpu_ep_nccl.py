@@ -41,9 +41,16 @@ def _worker(rank, world, port, ret):
         # the ranged variant (stage 2 in 4 column ranges, reduce-scatters issued beside it) agrees
         out4 = ep.ep_fused_moe(*args, overlap_chunks=4)
         assert float((out4.float() - out.float()).abs().max()) <= 0.04 * float(out.float().pow(2).mean().sqrt())
+        # the peer-memory combine (push of the produced rows + fixed-order sum) agrees with the reduce-scatter up to
+        # fp32 summation order, twice in a row (the second call reuses the mapped buffers)
+        for _ in range(2):
+            outp = ep.ep_fused_moe(*args, exchange="p2p")
+            sp = moe_oracle.error_stats(outp.cpu(), out.cpu())
+            assert not sp["has_nan"] and sp["n_diff"] <= 1e-3 * sp["numel"] and sp["max_abs_over_rms"] <= 0.02, sp
         torch.cuda.synchronize()
         aiter_b200.check_device_status()
         ret[rank] = out.cpu()
+        ret[rank + world] = outp.cpu()
     finally:
         dist.destroy_process_group()
 
@@ -57,10 +64,10 @@ def test_ep_two_gpus_matches_oracle():
     c = inputs.make_config("cfg4", seed=0, M=512)
     ref = moe_oracle.fused_moe_ref(c["x"], c["w1_q"], c["w1_scale"], c["w2_q"], c["w2_scale"],
                                    c["topk_weight"], c["topk_ids"])
-    out = torch.cat([ret[0], ret[1]], dim=0)
-    s = moe_oracle.error_stats(out, ref)
-    print("ep2:", s)
-    # 2M outputs: one flipped final rounding on a large element exceeds 2 % of RMS by itself, so the
-    # bound is on everything that is not an exact one-ulp neighbour of the reference
-    assert not s["has_nan"] and s["frac_within"] >= 0.995, s
-    assert s["max_abs_excl_one_ulp_over_rms"] <= 0.02 and s["max_abs_over_rms"] <= 0.04, s
+    for tag, out in (("reduce-scatter", torch.cat([ret[0], ret[1]], dim=0)), ("peer push", torch.cat([ret[2], ret[3]], dim=0))):
+        s = moe_oracle.error_stats(out, ref)
+        print("ep2", tag, s)
+        # 2M outputs: one flipped final rounding on a large element exceeds 2 % of RMS by itself, so the
+        # bound is on everything that is not an exact one-ulp neighbour of the reference
+        assert not s["has_nan"] and s["frac_within"] >= 0.995, (tag, s)
+        assert s["max_abs_excl_one_ulp_over_rms"] <= 0.02 and s["max_abs_over_rms"] <= 0.04, (tag, s)
