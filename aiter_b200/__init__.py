@@ -15,6 +15,7 @@ from .fused_moe import (  # noqa: F401
     moe_sorting,
     moe_sorting_get_workspace_size,
     per_group_quant_hip,
+    per_tensor_quant_hip,
     per_token_quant_hip,
 )
 
@@ -23,5 +24,5 @@ from .topk import biased_grouped_topk, fused_topk, topk_softmax  # noqa: F401,E4
 __all__ = [
     "biased_grouped_topk", "fused_topk", "topk_softmax",
     "ActivationType", "QuantType", "dtypes", "fused_moe", "fused_moe_", "shuffle_weight", "moe_sorting",
-    "moe_sorting_get_workspace_size", "get_hip_quant", "per_group_quant_hip", "per_token_quant_hip", "check_device_status",
+    "moe_sorting_get_workspace_size", "get_hip_quant", "per_group_quant_hip", "per_token_quant_hip", "per_tensor_quant_hip", "check_device_status",
 ]

@@ -50,6 +50,7 @@ _SIGNATURES = {
     "b200_biased_grouped_topk": (ctypes.c_int, [_T] * 4 + [ctypes.c_int] * 3 + [ctypes.c_float, ctypes.c_void_p]),
     "b200_topk_softmax": (ctypes.c_int, [_T] * 4 + [ctypes.c_int, ctypes.c_void_p]),
     "b200_moe_finalize": (ctypes.c_int, [_T] * 2 + [ctypes.c_void_p]),
+    "b200_moe_quant_per_tensor": (ctypes.c_int, [_T] * 6 + [ctypes.c_void_p]),
     "b200_ep_push_partials": (ctypes.c_int, [_T] * 3 + [ctypes.c_int] * 3 + [ctypes.c_void_p]),
     "b200_ep_combine": (ctypes.c_int, [_T] * 4 + [ctypes.c_int] * 3 + [ctypes.c_void_p]),
     "b200_ep_enable_peer_access": (ctypes.c_int, [ctypes.c_int] * 2),

@@ -23,6 +23,8 @@ void launch_moe_sorting_noalloc(const aiter_tensor_t*, const aiter_tensor_t*, ai
                                 const aiter_tensor_t*, aiter_tensor_t*, cudaStream_t);
 void launch_quant_1x128(aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*, cudaStream_t);
 void launch_quant_per_token(aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*, const aiter_tensor_t*, cudaStream_t);
+void launch_quant_per_tensor(aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*,
+                             const aiter_tensor_t*, cudaStream_t);
 void launch_moe_stage1(const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*,
                        const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*,
                        aiter_tensor_t*, aiter_tensor_t*, int, const aiter_tensor_t*, int, cudaStream_t);
@@ -206,6 +208,16 @@ B200_EXPORT int b200_moe_finalize(aiter_tensor_t* out, const aiter_tensor_t* acc
         B200_CHECK(acc != nullptr, "acc must not be NULL");
         DeviceGuard g(acc->device_id);
         launch_finalize(out, acc, (cudaStream_t)stream);
+    });
+}
+
+B200_EXPORT int b200_moe_quant_per_tensor(aiter_tensor_t* out, const aiter_tensor_t* input, aiter_tensor_t* scale,
+                                          aiter_tensor_t* amax, aiter_tensor_t* row_scales,
+                                          const aiter_tensor_t* row_limit, void* stream) {
+    return safe_call([&] {
+        B200_CHECK(input != nullptr, "input must not be NULL");
+        DeviceGuard g(input->device_id);
+        launch_quant_per_tensor(out, input, scale, amax, row_scales, row_limit, (cudaStream_t)stream);
     });
 }
 

@@ -6,6 +6,8 @@
 //
 // 16 lanes own one 128-element group (8 bf16 = one 16-byte load each), two groups per warp.
 
+#include <algorithm>
+
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
@@ -102,7 +104,88 @@ __global__ void __launch_bounds__(256) quant_per_token_kernel(const uint4* __res
     if (threadIdx.x == 0) scales[row] = scale;
 }
 
+// Per-tensor dynamic FP8 quantisation (QuantType.per_Tensor; torch twin per_tensor_quant, aiter/ops/quant.py:318-328:
+// scale = max|x| / 448 and codes = RNE_e4m3(x / scale), both IEEE divisions, no zero guard). Two passes:
+// the maximum over the rows below *row_limit goes to amax[0] (non-negative floats order like their bit patterns,
+// so an integer atomicMax does it), then every row is converted with the one scale, which is also written to
+// scale[0] and, if asked, once per row to row_scales (the GEMM kernels take one activation scale per row).
+__global__ void __launch_bounds__(256) amax_kernel(const uint4* __restrict__ x, int64_t rows, int cols8,
+                                                   const int* __restrict__ row_limit, unsigned int* __restrict__ amax) {
+    const int64_t limit = row_limit ? min((int64_t)*row_limit, rows) : rows;
+    const int64_t n = limit * cols8;
+    float m = 0.f;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const uint4 raw = __ldg(x + i);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 f = __bfloat1622float2(h[k]);
+            m = fmaxf(m, fmaxf(fabsf(f.x), fabsf(f.y)));
+        }
+    }
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+    if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(amax, __float_as_uint(m));
+}
+
+__global__ void __launch_bounds__(256) quant_per_tensor_kernel(const uint4* __restrict__ x, uint2* __restrict__ q,
+                                                               float* __restrict__ scale_out, float* __restrict__ row_scales,
+                                                               int64_t rows, int cols8, const int* __restrict__ row_limit,
+                                                               const unsigned int* __restrict__ amax) {
+    const int64_t limit = row_limit ? min((int64_t)*row_limit, rows) : rows;
+    const float scale = __fdiv_rn(__uint_as_float(*amax), 448.0f);
+    if (blockIdx.x == 0 && threadIdx.x == 0) scale_out[0] = scale;
+    const int64_t n = limit * cols8;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const uint4 raw = __ldg(x + i);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        uint32_t w[2];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const float2 a = __bfloat1622float2(h[2 * k]), b = __bfloat1622float2(h[2 * k + 1]);
+            const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(a.x, scale), __fdiv_rn(a.y, scale)),
+                                                         __NV_SATFINITE, __NV_E4M3);
+            const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(b.x, scale), __fdiv_rn(b.y, scale)),
+                                                         __NV_SATFINITE, __NV_E4M3);
+            w[k] = lo | (hi << 16);
+        }
+        q[i] = make_uint2(w[0], w[1]);
+    }
+    if (row_scales)
+        for (int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; r < rows; r += (int64_t)gridDim.x * blockDim.x)
+            row_scales[r] = scale;
+}
+
 }  // namespace
+
+void launch_quant_per_tensor(aiter_tensor_t* out, const aiter_tensor_t* input, aiter_tensor_t* scale, aiter_tensor_t* amax,
+                             aiter_tensor_t* row_scales, const aiter_tensor_t* row_limit, cudaStream_t stream) {
+    check_tensor(input, "input", AITER_DTYPE_bf16, 2);
+    check_tensor(out, "out", AITER_DTYPE_fp8, 2);
+    check_tensor(scale, "scale", AITER_DTYPE_fp32, -1);
+    check_tensor(amax, "amax", AITER_DTYPE_fp32, -1);
+    const int64_t rows = input->shape[0], cols = input->shape[1];
+    B200_CHECK(cols % 8 == 0 && cols >= 8, "row length must be a multiple of 8, got ", cols);
+    B200_CHECK(out->shape[0] == rows && out->shape[1] == cols, "out must have the shape of input");
+    B200_CHECK(scale->numel_ >= 1 && amax->numel_ >= 1, "scale and amax need one element each");
+    B200_CHECK(((uintptr_t)input->ptr & 15) == 0 && ((uintptr_t)out->ptr & 7) == 0, "input must be 16-byte and out 8-byte aligned");
+    if (row_scales) {
+        check_tensor(row_scales, "row_scales", AITER_DTYPE_fp32, -1);
+        B200_CHECK((int64_t)row_scales->numel_ >= rows, "row_scales needs one element per row");
+    }
+    if (row_limit) check_tensor(row_limit, "row_limit", AITER_DTYPE_i32, -1);
+    B200_CUDA(cudaMemsetAsync(amax->ptr, 0, sizeof(float), stream));
+    if (rows == 0) return;
+    const int64_t n = rows * (cols / 8);
+    const int grid = (int)std::min<int64_t>((n + 255) / 256, (int64_t)sm_count(input->device_id) * 8);
+    amax_kernel<<<grid, 256, 0, stream>>>((const uint4*)input->ptr, rows, (int)(cols / 8),
+                                          row_limit ? (const int*)row_limit->ptr : nullptr, (unsigned int*)amax->ptr);
+    quant_per_tensor_kernel<<<grid, 256, 0, stream>>>((const uint4*)input->ptr, (uint2*)out->ptr, (float*)scale->ptr,
+                                                      row_scales ? (float*)row_scales->ptr : nullptr, rows, (int)(cols / 8),
+                                                      row_limit ? (const int*)row_limit->ptr : nullptr,
+                                                      (const unsigned int*)amax->ptr);
+    B200_CUDA(cudaGetLastError());
+}
 
 void launch_quant_per_token(aiter_tensor_t* out, const aiter_tensor_t* input, aiter_tensor_t* scales,
                             const aiter_tensor_t* row_limit, cudaStream_t stream) {

@@ -156,13 +156,38 @@ def per_token_quant_hip(x, scale=None, quant_dtype=dtypes.fp8, row_limit=None):
     return y.view(x.shape), y_scale.view(*x.shape[:-1], 1)
 
 
+def per_tensor_quant_hip(x, scale=None, quant_dtype=dtypes.fp8, num_rows=None, num_rows_factor=1, row_limit=None,
+                         want_row_scales=False):
+    """Per-tensor dynamic FP8 quantisation, signature of aiter/ops/quant.py:628-645.
+    x [..., C] bf16 -> (codes e4m3, scale [1] fp32). ``row_limit``: optional device int32 [1], rows at or past it
+    take no part; ``want_row_scales`` also returns the scale repeated once per row (what the GEMM kernels read)."""
+    if scale is not None or num_rows is not None:
+        raise NotImplementedError("per_tensor_quant_hip: static scale / num_rows are not supported")
+    if quant_dtype != dtypes.fp8:
+        raise NotImplementedError("per_tensor_quant_hip: only quant_dtype=fp8 (e4m3fn) is supported")
+    if x.dtype != dtypes.bf16:
+        raise NotImplementedError(f"per_tensor_quant_hip: input must be bf16, got {x.dtype}")
+    x = x.contiguous()
+    x2 = x.view(-1, x.shape[-1])
+    y = torch.empty(x2.shape, dtype=dtypes.fp8, device=x.device)
+    y_scale = torch.empty((1,), dtype=dtypes.fp32, device=x.device)
+    amax = torch.empty((1,), dtype=dtypes.fp32, device=x.device)
+    rows = torch.empty((x2.shape[0],), dtype=dtypes.fp32, device=x.device) if want_row_scales else None
+    _lib.call("b200_moe_quant_per_tensor", y, x2, y_scale, amax, rows, row_limit, device=x.device)
+    if want_row_scales:
+        return y.view(x.shape), y_scale, rows
+    return y.view(x.shape), y_scale
+
+
 def get_hip_quant(qType):
     """aiter/ops/quant.py:367-387, restricted to the FP8 paths built here."""
     qType = quant_remap.get(QuantType(qType), QuantType(qType))
     if qType == QuantType.per_Token:
         return per_token_quant_hip
+    if qType == QuantType.per_Tensor:
+        return per_tensor_quant_hip
     if qType != QuantType.per_1x128:
-        raise NotImplementedError(f"get_hip_quant: only per_1x128 / per_128x128 / per_Token are supported, got {qType!r}")
+        raise NotImplementedError(f"get_hip_quant: only per_1x128 / per_128x128 / per_Token / per_Tensor are supported, got {qType!r}")
     return per_group_quant_hip
 
 
@@ -223,13 +248,19 @@ def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, 
         topk_ids, topk_weight, global_E, model_dim, dtypes.bf16, GEMM_BLOCK_M, expert_mask,
         num_local_tokens, 0, False, want_moe_buf=False)
     _mark(timers, "quant")
-    per_token = QuantType(quant_type) == QuantType.per_Token
+    # per_Tensor runs through the per_Token kernels: the one activation scale is repeated per row, the one weight
+    # scale per expert is repeated per output channel (the reference dequantises both types the same way,
+    # aiter/fused_moe.py:3583-3585, 3729-3731)
+    per_tensor = QuantType(quant_type) == QuantType.per_Tensor
+    per_token = per_tensor or QuantType(quant_type) == QuantType.per_Token
     act = int(ActivationType(activation))
     w_stage1 = sorted_weights if doweight_stage1 else None   # aiter/fused_moe.py:3651-3652
     dw2 = 0 if doweight_stage1 else 1
     qt = int(QuantType.per_Token if per_token else QuantType.per_1x128)
     if hidden_states.dtype == dtypes.fp8:
         a1, a1_s = hidden_states.contiguous(), a1_scale.contiguous().view(M, -1)
+    elif per_tensor:
+        a1, _scale, a1_s = per_tensor_quant_hip(hidden_states, want_row_scales=True)
     elif per_token:
         a1, a1_s = per_token_quant_hip(hidden_states)
     else:
@@ -247,7 +278,11 @@ def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, 
         _mark(timers, "requant")
         a2 = torch.empty((P, inter_dim), dtype=dtypes.fp8, device=device)
         a2_s = torch.empty((P,), dtype=dtypes.fp32, device=device)
-        _lib.call("b200_moe_quant_per_token", a2, a2_bf16, a2_s, num_valid_ids, device=device)
+        if per_tensor:
+            _lib.call("b200_moe_quant_per_tensor", a2, a2_bf16, torch.empty((1,), dtype=dtypes.fp32, device=device),
+                      torch.empty((1,), dtype=dtypes.fp32, device=device), a2_s, num_valid_ids, device=device)
+        else:
+            _lib.call("b200_moe_quant_per_token", a2, a2_bf16, a2_s, num_valid_ids, device=device)
     else:
         a2 = torch.empty((P, inter_dim), dtype=dtypes.fp8, device=device)
         a2_s = torch.empty((P, inter_dim // 128), dtype=dtypes.fp32, device=device)
@@ -332,10 +367,10 @@ def fused_moe(
     ``block_size_M`` is accepted and ignored: the GEMM row tile is fixed at 128, which only
     changes how the routes are padded, not the result."""
     quant_type = quant_remap.get(QuantType(quant_type), QuantType(quant_type))
-    if quant_type not in (QuantType.per_1x128, QuantType.per_Token):
+    if quant_type not in (QuantType.per_1x128, QuantType.per_Token, QuantType.per_Tensor):
         raise NotImplementedError(
             f"fused_moe: quant_type={QuantType(quant_type)!r} is not supported; this build covers "
-            "QuantType.per_1x128 / per_128x128 (FP8 block scale) and QuantType.per_Token (FP8)")
+            "QuantType.per_1x128 / per_128x128 (FP8 block scale), QuantType.per_Token and QuantType.per_Tensor (FP8)")
     if ActivationType(activation) not in (ActivationType.Silu, ActivationType.Gelu):
         raise NotImplementedError(f"fused_moe: activation={ActivationType(activation)!r} is not supported (Silu, Gelu)")
     _check_unsupported(
@@ -379,6 +414,12 @@ def fused_moe(
         raise ValueError("fused_moe: topk_weight must be float32")
     if topk_ids.dtype != dtypes.i32:
         raise ValueError("fused_moe: topk_ids must be int32")
+    if quant_type == QuantType.per_Tensor:
+        if hidden_states.dtype == dtypes.fp8:
+            a1_scale = a1_scale.to(dtypes.fp32).reshape(-1)[:1].expand(M).contiguous()
+        # one scale per expert -> one per output channel, the layout the per_Token kernels read
+        w1_scale = w1_scale.to(dtypes.fp32).reshape(E, 1).expand(E, 2 * inter_dim)
+        w2_scale = w2_scale.to(dtypes.fp32).reshape(E, 1).expand(E, model_dim)
     if M == 0:   # nothing to compute: the reference allocates the same empty result (aiter/fused_moe.py:579-619)
         return torch.empty((0, model_dim), dtype=dtype, device=hidden_states.device)
     return fused_moe_stages(hidden_states, w1.contiguous(), w2.contiguous(), topk_weight, topk_ids,

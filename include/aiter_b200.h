@@ -117,6 +117,16 @@ int b200_moe_quant_1x128(aiter_tensor_t* out, const aiter_tensor_t* input, aiter
 int b200_moe_quant_per_token(aiter_tensor_t* out, const aiter_tensor_t* input, aiter_tensor_t* scales,
                              const aiter_tensor_t* row_limit, void* stream);
 
+/* Dynamic per-tensor FP8 e4m3 quantisation (QuantType.per_Tensor): scale = max|x| / 448, codes = RNE(x / scale).
+ * Replaces dynamic_per_tensor_quant behind per_tensor_quant_hip (aiter/ops/quant.py:628-645) with the rounding
+ * sequence of per_tensor_quant (aiter/ops/quant.py:318-328; like it, no guard for an all-zero tensor).
+ *   input [R,C] bf16 -> out [R,C] fp8, scale [1] fp32; amax: [1] fp32 scratch word, cleared by the call;
+ *   row_scales: optional [R] fp32, receives the scale once per row (the per_Token GEMM kernels take one scale per
+ *   row); row_limit: optional [1] i32 on the device, rows >= it take no part (padded tail of a sorted buffer) */
+int b200_moe_quant_per_tensor(aiter_tensor_t* out, const aiter_tensor_t* input, aiter_tensor_t* scale,
+                              aiter_tensor_t* amax, aiter_tensor_t* row_scales, const aiter_tensor_t* row_limit,
+                              void* stream);
+
 /* Stage 1: grouped gate/up GEMM over the sorted blocks + SiLU(gate)*up + bf16 rounding +
  * 1x128 FP8 requantisation.  Replaces ck_moe_stage1 followed by the a2 quant
  * (csrc/ck_gemm_moe_2stages_codegen/gemm_moe_ck2stages.cu:68-137, aiter/fused_moe.py:3220-3336).

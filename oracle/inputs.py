@@ -16,6 +16,8 @@ import torch
 from .moe_oracle import (FP8, biased_grouped_topk_ref, quant_per_token, quant_weight_128x128,
                          softmax_topk_ref)
 
+# per_Tensor weights: one scale per expert (op_tests/test_moe_2stage.py:160-164, pertoken_quant over w.view(E, -1))
+
 # name -> dict(M, H, I, E, topk, routing)
 CONFIGS = {
     # tiny layer the reference's torch oracle runs on CPU
@@ -28,6 +30,8 @@ CONFIGS = {
     "cfg3": dict(M=4096, H=4096, I=14336, E=8, topk=2, routing="softmax", quant="per_token"),
     # the tiny layer with per-token activation scales and per-output-channel weight scales
     "cfg0_pt": dict(M=32, H=1024, I=512, E=8, topk=2, routing="softmax", quant="per_token"),
+    # the tiny layer with one activation scale per tensor and one weight scale per expert
+    "cfg0_ptensor": dict(M=32, H=1024, I=512, E=8, topk=2, routing="softmax", quant="per_tensor"),
     # Qwen3-235B-A22B shaped, skewed routing (M is swept by the caller)
     "cfg4": dict(M=1024, H=4096, I=1536, E=128, topk=8, routing="zipf"),
     # DeepSeek-V3 dimensions with few experts: cheap enough for CPU goldens
@@ -65,19 +69,24 @@ def make_routing(kind, M, E, topk, seed, device="cpu"):
     return w.to(device), ids.to(device)
 
 
-def make_weights(E, N, K, seed, device="cpu", experts_per_chunk=1, per_token=False):
+def make_weights(E, N, K, seed, device="cpu", experts_per_chunk=1, per_token=False, per_tensor=False):
     """[E,N,K] ~ N(0, 1/sqrt(K)) quantised to e4m3 per 128x128 block with
     scale = amax/448 (op_tests/test_moe_2stage.py:184-208), or per output channel
     (scales [E,N,1]) for QuantType.per_Token (:213-214)."""
     g = _gen(seed, device)
     q = torch.empty((E, N, K), dtype=FP8, device=device)
-    s = (torch.empty((E, N, 1), dtype=torch.float32, device=device) if per_token else
+    s = (torch.empty((E, 1), dtype=torch.float32, device=device) if per_tensor else
+         torch.empty((E, N, 1), dtype=torch.float32, device=device) if per_token else
          torch.empty((E, N // 128, K // 128), dtype=torch.float32, device=device))
     std = 1.0 / math.sqrt(K)
     for e0 in range(0, E, experts_per_chunk):
         e1 = min(E, e0 + experts_per_chunk)
         w = torch.randn((e1 - e0, N, K), generator=g, dtype=torch.float32, device=device) * std
-        qe, se = quant_per_token(w) if per_token else quant_weight_128x128(w)
+        if per_tensor:
+            qe, se = quant_per_token(w.view(e1 - e0, -1))
+            qe = qe.view(e1 - e0, N, K)
+        else:
+            qe, se = quant_per_token(w) if per_token else quant_weight_128x128(w)
         q[e0:e1] = qe
         s[e0:e1] = se
     return q, s
@@ -95,9 +104,9 @@ def make_config(name, seed=0, device="cpu", M=None, E=None):
         cfg["E"] = E
     M_, H, I, E_, topk = cfg["M"], cfg["H"], cfg["I"], cfg["E"], cfg["topk"]
     x = torch.randn((M_, H), generator=_gen(seed), dtype=torch.float32).to(torch.bfloat16)
-    pt = cfg.get("quant") == "per_token"
-    w1_q, w1_s = make_weights(E_, 2 * I, H, seed + 1, device, per_token=pt)
-    w2_q, w2_s = make_weights(E_, H, I, seed + 2, device, per_token=pt)
+    pt, pten = cfg.get("quant") == "per_token", cfg.get("quant") == "per_tensor"
+    w1_q, w1_s = make_weights(E_, 2 * I, H, seed + 1, device, per_token=pt, per_tensor=pten)
+    w2_q, w2_s = make_weights(E_, H, I, seed + 2, device, per_token=pt, per_tensor=pten)
     tw, ti = make_routing(cfg["routing"], M_, E_, topk, seed)
     return dict(x=x.to(device), w1_q=w1_q, w1_scale=w1_s, w2_q=w2_q, w2_scale=w2_s,
                 topk_weight=tw.to(device), topk_ids=ti.to(device), cfg=cfg)

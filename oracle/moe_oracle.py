@@ -59,6 +59,14 @@ def quant_per_token(x: torch.Tensor):
 
 
 # --------------------------------------------------------------------------- sorting
+def quant_per_tensor(x: torch.Tensor):
+    """per_tensor_quant (aiter/ops/quant.py:318-328): one scale = max|x| / 448 for the whole tensor, codes =
+    (x / scale).to(e4m3); no guard for an all-zero tensor. Returns (codes, scale [1])."""
+    x32 = x.to(torch.float32)
+    scale = torch.abs(x32).max() / 448.0
+    return (x32 / scale).to(FP8), scale.view(1).to(torch.float32)
+
+
 def moe_sorting_ref(topk_ids, topk_weights, num_experts, block_size,
                     expert_mask=None, num_local_tokens=None):
     """op_tests/test_moe_sorting.py:45-99 (run_torch_moe_sorting).
@@ -114,8 +122,8 @@ def _dequant_expert(w_q_e, w_s_e, per_token=False):
     """aiter/fused_moe.py:3589-3594: w.view(N/128,128,K/128,128) * scale.view(N/128,1,K/128,1);
     per_Token (:3583-3585): w * scale.view(N, 1)."""
     N, K = w_q_e.shape
-    if per_token:
-        return w_q_e.to(torch.float32) * w_s_e.reshape(N, 1)
+    if per_token:   # [N] scales per output channel, or one scale for the expert (per_Tensor)
+        return w_q_e.to(torch.float32) * w_s_e.reshape(-1, 1)
     w = w_q_e.to(torch.float32).view(N // 128, 128, K // 128, 128)
     w = w * w_s_e.reshape(N // 128, 1, K // 128, 1)
     return w.view(N, K)
@@ -133,7 +141,7 @@ def moe_stage1_ref(a1_q, a1_scale, w1_q, w1_scale, topk_weight, topk_ids, inter_
     E, N, _ = w1_q.shape
     hidden = a1_q.to(torch.float32)
     if per_token:   # aiter/fused_moe.py:3583-3585: hidden_states * a1_scale with a1_scale [M, 1]
-        hidden = hidden * a1_scale.view(M, 1)
+        hidden = hidden * a1_scale.reshape(-1, 1)   # [M,1], or [1] for per_Tensor
     else:
         s = a1_scale.view(M, -1, 1).repeat(1, 1, H // a1_scale.view(M, -1).shape[1]).view(M, -1)
         hidden = hidden * s
@@ -168,7 +176,7 @@ def moe_stage2_ref(a2_q, a2_scale, w2_q, w2_scale, topk_weight, topk_ids,
     E, H, I = w2_q.shape
     hidden = a2_q.to(torch.float32).view(M, topk, I)
     if per_token:   # aiter/fused_moe.py:3729-3731: a2_scale [M, topk, 1]
-        hidden = hidden * a2_scale.view(M, topk, 1)
+        hidden = hidden * (a2_scale.reshape(1, 1, 1) if a2_scale.numel() == 1 else a2_scale.view(M, topk, 1))
     else:
         s = a2_scale.view(M, topk, -1, 1).repeat(1, 1, 1, 128).view(M, topk, -1)
         hidden = hidden * s
@@ -187,7 +195,7 @@ def moe_stage2_ref(a2_q, a2_scale, w2_q, w2_scale, topk_weight, topk_ids,
 def fused_moe_ref(x, w1_q, w1_scale, w2_q, w2_scale, topk_weight, topk_ids,
                   expert_mask=None, dtype=torch.bfloat16, return_stages=False,
                   a1_q=None, a1_scale=None, per_token=False, activation="silu",
-                  doweight_stage1=False):
+                  doweight_stage1=False, per_tensor=False):
     """The pipeline of op_tests/test_moe_2stage.py (per_128x128 branch):
     a1 quant :237-242 -> torch_moe_stage1 :397-416 -> a2 quant :419-423 ->
     torch_moe_stage2 :448-460.  ``expert_mask`` follows torch_moe
@@ -196,17 +204,19 @@ def fused_moe_ref(x, w1_q, w1_scale, w2_q, w2_scale, topk_weight, topk_ids,
     I = w2_q.shape[2]
     ids = local_expert_ids(topk_ids, expert_mask)
     quant = quant_per_token if per_token else quant_1x128   # per_Token: op_tests/test_moe_2stage.py:264,446
+    if per_tensor:   # per_Tensor shares per_Token's dequantisation (aiter/fused_moe.py:3583-3585, 3729-3731)
+        quant, per_token = quant_per_tensor, True
     if a1_q is None:
         a1_q, a1_scale = quant(x)
     out1 = moe_stage1_ref(a1_q, a1_scale, w1_q, w1_scale, topk_weight, ids, I, dtype=dtype, per_token=per_token,
                           activation=activation, doweight=doweight_stage1)
     a2_q, a2_scale = quant(out1.view(-1, I))
     topk = topk_ids.shape[1]
-    out = moe_stage2_ref(a2_q.view(M, topk, I), a2_scale.view(M, topk, -1), w2_q, w2_scale,
+    out = moe_stage2_ref(a2_q.view(M, topk, I), a2_scale if per_tensor else a2_scale.view(M, topk, -1), w2_q, w2_scale,
                          topk_weight, ids, dtype=dtype, per_token=per_token, doweight=not doweight_stage1)
     if return_stages:
-        return out, dict(a1_q=a1_q, a1_scale=a1_scale, out1=out1,
-                         a2_q=a2_q.view(M, topk, I), a2_scale=a2_scale.view(M, topk, -1))
+        return out, dict(a1_q=a1_q, a1_scale=a1_scale, out1=out1, a2_q=a2_q.view(M, topk, I),
+                         a2_scale=a2_scale if per_tensor else a2_scale.view(M, topk, -1))
     return out
 
 

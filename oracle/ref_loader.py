@@ -80,7 +80,7 @@ def available(root=DEFAULT_ROOT):
 
 def load(root=DEFAULT_ROOT):
     """Returns a namespace with the unmodified reference functions:
-    torch_moe_stage1, torch_moe_stage2, pertoken_quant, run_torch_moe_sorting,
+    torch_moe_stage1, torch_moe_stage2, pertoken_quant, per_tensor_quant, run_torch_moe_sorting,
     biased_grouped_topk_torch."""
     dtypes = _dtypes_ns()
     aiter_ns = types.SimpleNamespace(
@@ -98,14 +98,14 @@ def load(root=DEFAULT_ROOT):
     exec(_extract(os.path.join(root, "aiter", "fused_moe.py"),
                   ["get_inter_dim", "torch_moe_stage1", "torch_moe_stage2", "torch_moe_act"]), ns)
     exec(_extract(os.path.join(root, "aiter", "ops", "quant.py"),
-                  ["get_dtype_max", "pertoken_quant"]), ns)
+                  ["get_dtype_max", "pertoken_quant", "per_tensor_quant"]), ns)
     exec(_extract(os.path.join(root, "op_tests", "test_moe_sorting.py"),
                   ["run_torch_moe_sorting"]), ns)
     exec(_extract(os.path.join(root, "aiter", "ops", "topk.py"),
                   ["biased_grouped_topk_torch"]), ns)
     aiter_ns.pertoken_quant = ns["pertoken_quant"]
     out = types.SimpleNamespace(**{k: ns[k] for k in (
-        "torch_moe_stage1", "torch_moe_stage2", "pertoken_quant", "run_torch_moe_sorting",
+        "torch_moe_stage1", "torch_moe_stage2", "pertoken_quant", "per_tensor_quant", "run_torch_moe_sorting",
         "biased_grouped_topk_torch")})
     out.QuantType = QuantType
     out.ActivationType = ActivationType

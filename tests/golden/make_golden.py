@@ -16,6 +16,7 @@ Fixtures (numpy ``.npz``; bf16 stored as its uint16 bit pattern, e4m3 as uint8):
   cfg0_ep2.npz        the same layer split over 2 expert-parallel ranks (local ids + mask)
   dsv3_slice.npz      DeepSeek-V3 dimensions with 8 experts (M=16,H=7168,I=2048,topk=8)
   cfg0_per_token.npz  the tiny layer with QuantType.per_Token (row scales, per-output-channel weight scales)
+  cfg0_per_tensor.npz the tiny layer with QuantType.per_Tensor (one activation scale, one weight scale per expert)
   cfg0_variants.npz   the tiny layer with Gelu and/or doweight_stage1
   routing_dsv3.npz    biased_grouped_topk_torch (8 groups, top-4 groups, top-8, x2.5)
 """
@@ -89,14 +90,33 @@ def ref_pipeline_per_token(ref, x, w1_q, w1_s, w2_q, w2_s, tw, ids):
     return dict(a1_q=a1_q, a1_scale=a1_s, out1=out1, a2_q=a2_q, a2_scale=a2_s, out=out)
 
 
+def ref_pipeline_per_tensor(ref, x, w1_q, w1_s, w2_q, w2_s, tw, ids):
+    """op_tests/test_moe_2stage.py, QuantType.per_Tensor branch (:160-164 weights, torch_quant = per_tensor_quant for
+    the activations :264, :446)."""
+    M, H = x.shape
+    topk = ids.shape[1]
+    QT = ref.QuantType.per_Tensor
+    a1_q, a1_s = ref.per_tensor_quant(x, quant_dtype=FP8)
+    out1 = ref.torch_moe_stage1(a1_q, w1_q, w2_q, tw, ids, dtype=torch.bfloat16,
+                                activation=ref.ActivationType.Silu, quant_type=QT,
+                                a1_scale=a1_s, w1_scale=w1_s)
+    a2_q, a2_s = ref.per_tensor_quant(out1, quant_dtype=FP8)
+    a2_q = a2_q.view(M, topk, -1)
+    out = ref.torch_moe_stage2(a2_q, w1_q, w2_q, tw, ids, dtype=torch.bfloat16, quant_type=QT,
+                               w2_scale=w2_s, a2_scale=a2_s)
+    return dict(a1_q=a1_q, a1_scale=a1_s, out1=out1, a2_q=a2_q, a2_scale=a2_s, out=out)
+
+
 def layer_case(ref, name, fname):
     c = inputs.make_config(name, seed=0)
     pt = c["cfg"].get("quant") == "per_token"
-    pipe = ref_pipeline_per_token if pt else ref_pipeline
+    pten = c["cfg"].get("quant") == "per_tensor"
+    pipe = ref_pipeline_per_tensor if pten else ref_pipeline_per_token if pt else ref_pipeline
     r = pipe(ref, c["x"], c["w1_q"], c["w1_scale"], c["w2_q"], c["w2_scale"],
              c["topk_weight"], c["topk_ids"])
     out, st = moe_oracle.fused_moe_ref(c["x"], c["w1_q"], c["w1_scale"], c["w2_q"], c["w2_scale"],
-                                       c["topk_weight"], c["topk_ids"], return_stages=True, per_token=pt)
+                                       c["topk_weight"], c["topk_ids"], return_stages=True, per_token=pt,
+                                       per_tensor=pten)
     if pt:
         st = dict(st, a1_scale=st["a1_scale"].view(r["a1_scale"].shape), a2_scale=st["a2_scale"].view(r["a2_scale"].shape))
     for k in ("a1_q", "a1_scale", "out1", "a2_q", "a2_scale"):
@@ -191,6 +211,7 @@ def main():
     c0, r0 = layer_case(ref, "cfg0", "cfg0.npz")
     layer_case(ref, "dsv3_slice", "dsv3_slice.npz")
     layer_case(ref, "cfg0_pt", "cfg0_per_token.npz")
+    layer_case(ref, "cfg0_ptensor", "cfg0_per_tensor.npz")
 
     # ---- activation / weighting variants on the tiny layer (aiter/fused_moe.py:3651-3652, 3665-3681) ----
     var = {}

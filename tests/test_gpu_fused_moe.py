@@ -312,6 +312,23 @@ def test_per_token_layer_against_reference_fixture():
     assert_parity(out, from_bits(g["out"], torch.bfloat16), "cfg0 per_Token, fp8 input")
 
 
+def test_per_tensor_layer_against_reference_fixture():
+    """QuantType.per_Tensor (one activation scale per tensor, one weight scale per expert) on the tiny layer."""
+    g = load_golden("cfg0_per_tensor.npz")
+    c = to_dev(inputs.make_config("cfg0_ptensor", seed=0))
+    a1, a1s = aiter_b200.get_hip_quant(QT.per_Tensor)(c["x"])
+    assert np.array_equal(a1.cpu().view(torch.uint8).numpy(), g["a1_q"])
+    assert np.array_equal(a1s.cpu().numpy(), g["a1_scale"])
+    ref = from_bits(g["out"], torch.bfloat16)
+    out = aiter_b200.fused_moe(c["x"], c["w1_q"], c["w2_q"], c["topk_weight"], c["topk_ids"], quant_type=QT.per_Tensor,
+                               w1_scale=c["w1_scale"], w2_scale=c["w2_scale"])
+    assert_parity(out, ref, "cfg0 per_Tensor")
+    out = aiter_b200.fused_moe(a1, c["w1_q"], c["w2_q"], c["topk_weight"], c["topk_ids"], quant_type=QT.per_Tensor,
+                               w1_scale=c["w1_scale"], w2_scale=c["w2_scale"], a1_scale=a1s)
+    assert_parity(out, ref, "cfg0 per_Tensor, fp8 input")
+    aiter_b200.check_device_status()
+
+
 def test_mixtral_shape_per_token_sampled():
     """Config 3: M=4096, H=4096, I=14336, E=8, topk=2, per_Token FP8. Exact check of 24 sampled tokens."""
     c = to_dev(inputs.make_config("cfg3", seed=0, device=DEV))

@@ -72,7 +72,8 @@ def _check_layer(name, fname):
     assert int(c["w1_q"].view(torch.uint8).long().sum()) == int(g["w1_q_sum"])
     out, st = moe_oracle.fused_moe_ref(c["x"], c["w1_q"], c["w1_scale"], c["w2_q"], c["w2_scale"],
                                        c["topk_weight"], c["topk_ids"], return_stages=True,
-                                       per_token=c["cfg"].get("quant") == "per_token")
+                                       per_token=c["cfg"].get("quant") == "per_token",
+                                       per_tensor=c["cfg"].get("quant") == "per_tensor")
     assert np.array_equal(st["a1_q"].view(torch.uint8).numpy(), g["a1_q"])
     assert np.array_equal(st["a1_scale"].numpy().reshape(g["a1_scale"].shape), g["a1_scale"])
     # fp32 sgemm blocking may depend on the host's thread count: allow isolated 1-ulp flips
@@ -90,6 +91,10 @@ def test_layer_cfg0():
 
 def test_layer_cfg0_per_token():
     _check_layer("cfg0_pt", "cfg0_per_token.npz")
+
+
+def test_layer_cfg0_per_tensor():
+    _check_layer("cfg0_ptensor", "cfg0_per_tensor.npz")
 
 
 def test_layer_dsv3_slice():
