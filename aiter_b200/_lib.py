@@ -53,7 +53,9 @@ _SIGNATURES = {
     "b200_moe_quant_per_tensor": (ctypes.c_int, [_T] * 6 + [ctypes.c_void_p]),
     "b200_ep_push_partials": (ctypes.c_int, [_T] * 3 + [ctypes.c_int] * 3 + [ctypes.c_void_p]),
     "b200_ep_combine": (ctypes.c_int, [_T] * 4 + [ctypes.c_int] * 3 + [ctypes.c_void_p]),
-    "b200_ep_enable_peer_access": (ctypes.c_int, [ctypes.c_int] * 2),
+    "b200_ep_ipc_export": (ctypes.c_int, [_T, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64)]),
+    "b200_ep_ipc_open": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_int64)]),
+    "b200_ep_ipc_close": (ctypes.c_int, [ctypes.c_int64, ctypes.c_int]),
 }
 
 _lib = None

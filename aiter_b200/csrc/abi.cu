@@ -38,7 +38,9 @@ void launch_topk_softmax(aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*, cons
 void launch_ep_push(const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, int, int, int, cudaStream_t);
 void launch_ep_combine(aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, int, int, int,
                        cudaStream_t);
-void enable_peer_access(int, int);
+void ipc_export(const aiter_tensor_t*, void*, int64_t*);
+void ipc_open(const void*, int, int64_t*);
+void ipc_close(int64_t, int);
 
 namespace {
 
@@ -241,8 +243,16 @@ B200_EXPORT int b200_ep_combine(aiter_tensor_t* out, const aiter_tensor_t* acc, 
     });
 }
 
-B200_EXPORT int b200_ep_enable_peer_access(int device, int peer_device) {
-    return safe_call([&] { enable_peer_access(device, peer_device); });
+B200_EXPORT int b200_ep_ipc_export(const aiter_tensor_t* tensor, void* handle_out, int64_t* offset_out) {
+    return safe_call([&] { ipc_export(tensor, handle_out, offset_out); });
+}
+
+B200_EXPORT int b200_ep_ipc_open(const void* handle, int device, int64_t* ptr_out) {
+    return safe_call([&] { ipc_open(handle, device, ptr_out); });
+}
+
+B200_EXPORT int b200_ep_ipc_close(int64_t ptr, int device) {
+    return safe_call([&] { ipc_close(ptr, device); });
 }
 
 }  // extern "C"

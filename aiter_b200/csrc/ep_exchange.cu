@@ -22,6 +22,9 @@
 // Plain peer loads/stores only: no multimem, no cluster launch.
 
 #include <algorithm>
+#include <cstring>
+
+#include <cuda.h>
 
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -147,20 +150,55 @@ void launch_ep_combine(aiter_tensor_t* out, const aiter_tensor_t* acc, const ait
     B200_CUDA(cudaGetLastError());
 }
 
-// Lets kernels running on `device` read and write memory of `peer_device` (a mapping opened from another
-// process's allocation lives on the exporting GPU). Idempotent.
-void enable_peer_access(int device, int peer_device) {
-    if (device == peer_device) return;
-    DeviceGuard guard(device);
-    int can = 0;
-    B200_CUDA(cudaDeviceCanAccessPeer(&can, device, peer_device));
-    B200_CHECK(can == 1, "GPU ", device, " cannot access GPU ", peer_device, " as a peer");
-    cudaError_t e = cudaDeviceEnablePeerAccess(peer_device, 0);
-    if (e == cudaErrorPeerAccessAlreadyEnabled) {
-        cudaGetLastError();   // clear the sticky-free error state
-        return;
+// ---- mapping another process's receive buffer (CUDA IPC) --------------------------------------------------------
+// A mapping belongs to the device that was current when it was opened: a pointer opened under GPU b is not
+// usable by kernels of GPU a, even with peer access enabled between the two. Every rank therefore opens its
+// peers' handles with ITS OWN device current (cudaIpcMemLazyEnablePeerAccess sets up the peer mapping).
+
+// handle_out: 64 bytes (cudaIpcMemHandle_t) for the allocation that holds t; offset_out: t's byte offset in it.
+void ipc_export(const aiter_tensor_t* t, void* handle_out, int64_t* offset_out) {
+    check_tensor(t, "tensor", -1, -1);
+    B200_CHECK(handle_out != nullptr && offset_out != nullptr, "handle_out / offset_out must not be NULL");
+    B200_CHECK(t->ptr != nullptr, "tensor has no storage");
+    DeviceGuard guard(t->device_id);
+    using RangeFn = CUresult (*)(CUdeviceptr*, size_t*, CUdeviceptr);
+    static RangeFn range_fn = nullptr;
+    if (!range_fn) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        B200_CUDA(cudaGetDriverEntryPoint("cuMemGetAddressRange", &sym, cudaEnableDefault, &qres));
+        B200_CHECK(sym != nullptr && qres == cudaDriverEntryPointSuccess, "cuMemGetAddressRange is not available");
+        range_fn = reinterpret_cast<RangeFn>(sym);
     }
-    B200_CUDA(e);
+    CUdeviceptr base = 0;
+    size_t size = 0;
+    CUresult r = range_fn(&base, &size, (CUdeviceptr)(uintptr_t)t->ptr);
+    B200_CHECK(r == CUDA_SUCCESS, "cuMemGetAddressRange failed with code ", (int)r);
+    cudaIpcMemHandle_t h;
+    B200_CUDA(cudaIpcGetMemHandle(&h, (void*)(uintptr_t)base));
+    static_assert(sizeof(h) == 64, "cudaIpcMemHandle_t is 64 bytes");
+    memcpy(handle_out, &h, sizeof(h));
+    *offset_out = (int64_t)((uintptr_t)t->ptr - (uintptr_t)base);
+}
+
+// Opens a handle made by ipc_export in another process, for kernels of `device`.
+void ipc_open(const void* handle, int device, int64_t* ptr_out) {
+    B200_CHECK(handle != nullptr && ptr_out != nullptr, "handle / ptr_out must not be NULL");
+    DeviceGuard guard(device);
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, sizeof(h));
+    void* p = nullptr;
+    B200_CUDA(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    B200_CHECK(p != nullptr, "cudaIpcOpenMemHandle returned a null pointer");
+    cudaPointerAttributes attr;
+    B200_CUDA(cudaPointerGetAttributes(&attr, p));
+    B200_CHECK(attr.type == cudaMemoryTypeDevice, "the mapped pointer is not device memory (type ", (int)attr.type, ")");
+    *ptr_out = (int64_t)(uintptr_t)p;
+}
+
+void ipc_close(int64_t ptr, int device) {
+    DeviceGuard guard(device);
+    B200_CUDA(cudaIpcCloseMemHandle((void*)(uintptr_t)ptr));
 }
 
 }  // namespace b200

@@ -63,31 +63,43 @@ def _gpu_finalize(acc, dtype):
 class PeerExchange:
     """Receive buffers for the peer-memory combine, one set per (process group, rows per rank, model_dim).
 
-    Every rank allocates recv [world, m_local, H] fp32, exports it through CUDA IPC (the handle that
-    torch.multiprocessing uses to pass CUDA tensors between processes), maps the buffers of all other ranks
-    and keeps their addresses in a device array for the push kernel. Built once, on first use; building it is
-    a collective call (all ranks of the group must reach it)."""
+    Every rank allocates recv [world, m_local, H] fp32, exports the allocation through CUDA IPC, maps the
+    buffers of all other ranks and keeps their addresses in a device array for the push kernel. Built once,
+    on first use; building it is a collective call (all ranks of the group must reach it)."""
 
     _cache: dict = {}
 
     def __init__(self, group, m_local, H, device):
-        from torch.multiprocessing.reductions import reduce_tensor
+        import ctypes
         world, rank = dist.get_world_size(group), dist.get_rank(group)
+        self.device = device
         self.recv = torch.empty((world, m_local, H), dtype=torch.float32, device=device)
         self.flag = torch.zeros(1, dtype=torch.int32, device=device)
+        handle = ctypes.create_string_buffer(64)
+        offset = ctypes.c_int64(0)
+        _lib.call_plain("b200_ep_ipc_export", ctypes.byref(_lib.to_aiter(self.recv)), handle, ctypes.byref(offset))
         exported = [None] * world
-        dist.all_gather_object(exported, reduce_tensor(self.recv), group=group)
-        self.peers = []
+        dist.all_gather_object(exported, (handle.raw, int(offset.value)), group=group)
+        # every peer's buffer is mapped with THIS rank's device current: a mapping belongs to the device it was
+        # opened under, and the push kernel of this rank is what stores through it
+        self.mapped = []
+        addrs = []
         for r in range(world):
             if r == rank:
-                self.peers.append(self.recv)
-            else:
-                rebuild, args = exported[r]
-                t = rebuild(*args)      # lives on the exporting rank's GPU, mapped into this process
-                _lib.call_plain("b200_ep_enable_peer_access", int(device.index), int(t.device.index))
-                self.peers.append(t)
-        self.ptrs = torch.tensor([t.data_ptr() for t in self.peers], dtype=torch.int64, device=device)
+                addrs.append(self.recv.data_ptr())
+                continue
+            base = ctypes.c_int64(0)
+            _lib.call_plain("b200_ep_ipc_open", ctypes.create_string_buffer(exported[r][0], 64), int(device.index),
+                            ctypes.byref(base))
+            self.mapped.append(int(base.value))
+            addrs.append(int(base.value) + exported[r][1])
+        self.ptrs = torch.tensor(addrs, dtype=torch.int64, device=device)
         dist.barrier(group=group)       # nobody pushes into a buffer that is not mapped everywhere yet
+
+    def close(self):
+        for base in self.mapped:
+            _lib.call_plain("b200_ep_ipc_close", base, int(self.device.index))
+        self.mapped = []
 
     @classmethod
     def get(cls, group, m_local, H, device):

@@ -180,13 +180,18 @@ int b200_moe_finalize(aiter_tensor_t* out, const aiter_tensor_t* acc, void* stre
  *   The caller then runs any collective as a barrier, and
  *   b200_ep_combine: out[tl,:] (bf16/fp16 [m_local,H]) = round(sum over ranks r, ascending, that have a route of
  *     token t = rank*m_local + tl, of (r == rank ? acc[t,:] : recv[r,tl,:])).
- *   b200_ep_enable_peer_access: lets kernels on `device` access memory of `peer_device` (idempotent).
+ *   b200_ep_ipc_export / _open / _close: CUDA IPC for the receive buffers. export writes the 64-byte handle of the
+ *     allocation that holds `tensor` and the tensor's byte offset in it; open maps such a handle from another
+ *     process for kernels of `device` (the mapping belongs to the device that is current while it is opened, so
+ *     every rank opens its peers' handles under its own device) and returns the base address; close unmaps it.
  * No device-side waiting between ranks; rows that were not pushed are never read. */
 int b200_ep_push_partials(const aiter_tensor_t* acc, const aiter_tensor_t* topk_ids, const aiter_tensor_t* peer_recv,
                           int rank, int world, int experts_per_rank, void* stream);
 int b200_ep_combine(aiter_tensor_t* out, const aiter_tensor_t* acc, const aiter_tensor_t* recv,
                     const aiter_tensor_t* topk_ids, int rank, int world, int experts_per_rank, void* stream);
-int b200_ep_enable_peer_access(int device, int peer_device);
+int b200_ep_ipc_export(const aiter_tensor_t* tensor, void* handle_out, int64_t* offset_out);
+int b200_ep_ipc_open(const void* handle, int device, int64_t* ptr_out);
+int b200_ep_ipc_close(int64_t ptr, int device);
 
 /* DeepSeek-V3 style router: sigmoid scores, correction bias for the choice only, groups ranked by the sum
  * of their two best biased scores, top `topk_group` groups kept, top-k experts among them; weights are the

@@ -1,5 +1,6 @@
 """Expert parallelism over 2 GPUs (NCCL) against the single-GPU result; skipped with fewer than 2 devices."""
 
+import datetime
 import os
 import socket
 
@@ -25,7 +26,8 @@ def _worker(rank, world, port, ret):
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    # a short collective timeout: a rank that failed must not leave the other waiting for minutes
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=datetime.timedelta(seconds=120))
     try:
         import aiter_b200
         from aiter_b200 import ep
