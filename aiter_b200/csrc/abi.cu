@@ -38,6 +38,8 @@ void launch_topk_softmax(aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*, cons
 void launch_ep_push(const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, int, int, int, cudaStream_t);
 void launch_ep_combine(aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, int, int, int,
                        cudaStream_t);
+void launch_ep_dispatch(const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*,
+                        const aiter_tensor_t*, int, int, int, cudaStream_t);
 void ipc_export(const aiter_tensor_t*, void*, int64_t*);
 void ipc_open(const void*, int, int64_t*);
 void ipc_close(int64_t, int);
@@ -220,6 +222,17 @@ B200_EXPORT int b200_moe_quant_per_tensor(aiter_tensor_t* out, const aiter_tenso
         B200_CHECK(input != nullptr, "input must not be NULL");
         DeviceGuard g(input->device_id);
         launch_quant_per_tensor(out, input, scale, amax, row_scales, row_limit, (cudaStream_t)stream);
+    });
+}
+
+B200_EXPORT int b200_ep_dispatch(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale, const aiter_tensor_t* topk_ids,
+                                 const aiter_tensor_t* peer_a1, const aiter_tensor_t* peer_a1_scale, int rank, int world,
+                                 int experts_per_rank, void* stream) {
+    return safe_call([&] {
+        B200_CHECK(a1 != nullptr, "a1 must not be NULL");
+        DeviceGuard g(a1->device_id);
+        launch_ep_dispatch(a1, a1_scale, topk_ids, peer_a1, peer_a1_scale, rank, world, experts_per_rank,
+                           (cudaStream_t)stream);
     });
 }
 

@@ -67,6 +67,27 @@ __global__ void __launch_bounds__(kEpThreads) ep_push_kernel(const float4* __res
     __threadfence_system();   // the peer stores are performed before this kernel counts as complete
 }
 
+// Dispatch: the quantised row of every local token (codes + block scales) goes to the ranks that hold one of its
+// experts, this rank's own buffer included (its address is in the table like any other), at the token's global row.
+__global__ void __launch_bounds__(kEpThreads) ep_dispatch_kernel(const uint4* __restrict__ a1, const uint32_t* __restrict__ a1s,
+                                                                 const int* __restrict__ topk_ids,
+                                                                 const long long* __restrict__ peer_a1,
+                                                                 const long long* __restrict__ peer_a1s, int m_local, int H16,
+                                                                 int KB, int topk, int rank, int world, int experts_per_rank) {
+    for (int tl = blockIdx.x; tl < m_local; tl += gridDim.x) {
+        const unsigned long long m = touch_mask(topk_ids + (size_t)tl * topk, topk, experts_per_rank, world);
+        const size_t t = (size_t)rank * m_local + tl;
+        for (int r = 0; r < world; ++r) {
+            if (!((m >> r) & 1ull)) continue;
+            uint4* dq = reinterpret_cast<uint4*>(peer_a1[r]) + t * H16;
+            uint32_t* ds = reinterpret_cast<uint32_t*>(peer_a1s[r]) + t * KB;
+            for (int i = threadIdx.x; i < H16; i += kEpThreads) dq[i] = a1[(size_t)tl * H16 + i];
+            for (int i = threadIdx.x; i < KB; i += kEpThreads) ds[i] = a1s[(size_t)tl * KB + i];
+        }
+    }
+    __threadfence_system();
+}
+
 template <typename T2>
 __device__ __forceinline__ T2 to_pair(float a, float b);
 template <>
@@ -111,6 +132,30 @@ void check_common(const aiter_tensor_t* acc, const aiter_tensor_t* topk_ids, int
 }
 
 }  // namespace
+
+void launch_ep_dispatch(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale, const aiter_tensor_t* topk_ids,
+                        const aiter_tensor_t* peer_a1, const aiter_tensor_t* peer_a1_scale, int rank, int world,
+                        int experts_per_rank, cudaStream_t stream) {
+    check_tensor(a1, "a1", AITER_DTYPE_fp8, 2);
+    check_tensor(a1_scale, "a1_scale", AITER_DTYPE_fp32, 2);
+    check_tensor(topk_ids, "topk_ids", AITER_DTYPE_i32, 2);
+    check_tensor(peer_a1, "peer_a1", AITER_DTYPE_i64, 1);
+    check_tensor(peer_a1_scale, "peer_a1_scale", AITER_DTYPE_i64, 1);
+    const int64_t m_local = a1->shape[0], H = a1->shape[1], KB = a1_scale->shape[1];
+    B200_CHECK(a1_scale->shape[0] == m_local && topk_ids->shape[0] == m_local, "a1_scale / topk_ids rows must match a1");
+    B200_CHECK(world >= 1 && world <= kMaxWorld && rank >= 0 && rank < world, "bad rank/world: ", rank, "/", world);
+    B200_CHECK(experts_per_rank >= 1, "experts_per_rank must be positive");
+    B200_CHECK((int64_t)peer_a1->numel_ == world && (int64_t)peer_a1_scale->numel_ == world,
+               "peer tables need one address per rank");
+    B200_CHECK(H % 16 == 0 && ((uintptr_t)a1->ptr & 15) == 0, "rows must be 16-byte multiples and 16-byte aligned");
+    if (m_local == 0) return;
+    const int grid = (int)std::min<int64_t>(m_local, (int64_t)sm_count(a1->device_id) * 8);
+    ep_dispatch_kernel<<<grid, kEpThreads, 0, stream>>>((const uint4*)a1->ptr, (const uint32_t*)a1_scale->ptr,
+                                                       (const int*)topk_ids->ptr, (const long long*)peer_a1->ptr,
+                                                       (const long long*)peer_a1_scale->ptr, (int)m_local, (int)(H / 16),
+                                                       (int)KB, (int)topk_ids->shape[1], rank, world, experts_per_rank);
+    B200_CUDA(cudaGetLastError());
+}
 
 void launch_ep_push(const aiter_tensor_t* acc, const aiter_tensor_t* topk_ids, const aiter_tensor_t* peer_recv, int rank,
                     int world, int experts_per_rank, cudaStream_t stream) {

@@ -14,10 +14,12 @@ Reducing in fp32 keeps the result equal to the single-GPU one up to fp32 summati
 reference reaches the same end with an all-to-all dispatch/combine
 (op_tests/multigpu_tests/test_dispatch_combine.py:75-177, oracle run_ref :18-72).
 
-With ``exchange="p2p"`` step 3 is instead a push of the partial rows a rank really produced into the owning
-rank's memory over NVLink (CUDA IPC mappings, plain peer stores), a tiny all-reduce as the barrier, and a
-combine kernel that adds what arrived in a fixed rank order: rows of tokens without a route on the sending
-rank (with DeepSeek-V3's group-limited routing, half of them at 8 ranks) do not travel.
+With ``exchange="p2p"`` both exchanges go over NVLink peer memory (CUDA IPC mappings, plain peer stores) and
+ship only rows that are needed: step 1 stores a token's quantised row into the buffers of the ranks that hold
+one of its experts (the small routing table is still all-gathered, which doubles as the barrier), step 3 pushes
+the partial rows a rank really produced into the owning rank's memory, runs a tiny all-reduce as the barrier,
+and a combine kernel adds what arrived in a fixed rank order. With DeepSeek-V3's group-limited routing a token
+has routes on at most half of 8 ranks, so half of the rows of the dense collectives do not travel.
 
 The collectives go through ``torch.distributed`` so the same code runs on gloo/CPU ranks for the
 host-logic tests; ``local_layer`` is injectable for that purpose.
@@ -61,11 +63,13 @@ def _gpu_finalize(acc, dtype):
 
 
 class PeerExchange:
-    """Receive buffers for the peer-memory combine, one set per (process group, rows per rank, model_dim).
+    """Buffers for the peer-memory exchange, one set per (process group, rows per rank, model_dim).
 
-    Every rank allocates recv [world, m_local, H] fp32, exports the allocation through CUDA IPC, maps the
-    buffers of all other ranks and keeps their addresses in a device array for the push kernel. Built once,
-    on first use; building it is a collective call (all ranks of the group must reach it)."""
+    Every rank allocates ONE arena holding recv [world, m_local, H] fp32 (partial rows pushed to it), a1
+    [M, H] e4m3 and a1_scale [M, H/128] fp32 (token rows dispatched to it), exports the allocation through CUDA
+    IPC, maps the arenas of all other ranks and keeps the addresses of the three buffers on every rank in device
+    arrays for the kernels. Built once, on first use; building it is a collective call (all ranks of the group
+    must reach it)."""
 
     _cache: dict = {}
 
@@ -73,28 +77,53 @@ class PeerExchange:
         import ctypes
         world, rank = dist.get_world_size(group), dist.get_rank(group)
         self.device = device
-        self.recv = torch.empty((world, m_local, H), dtype=torch.float32, device=device)
+        M, kb = world * m_local, H // 128
+        align = lambda n: (n + 255) // 256 * 256
+        off_recv, off_a1 = 0, align(world * m_local * H * 4)
+        off_a1s = off_a1 + align(M * H)
+        total = off_a1s + align(M * kb * 4)
+        self.arena = torch.empty((total,), dtype=torch.uint8, device=device)
+        self.recv = self.arena[off_recv:off_recv + world * m_local * H * 4].view(torch.float32).view(world, m_local, H)
+        self.a1 = self.arena[off_a1:off_a1 + M * H].view(torch.float8_e4m3fn).view(M, H)
+        self.a1_scale = self.arena[off_a1s:off_a1s + M * kb * 4].view(torch.float32).view(M, kb)
         self.flag = torch.zeros(1, dtype=torch.int32, device=device)
+        # Export, exchange, map. A failure on any rank (no IPC in this environment, no peer access) is agreed on
+        # by all ranks before anybody raises, so that callers can fall back to the NCCL exchange together.
         handle = ctypes.create_string_buffer(64)
         offset = ctypes.c_int64(0)
-        _lib.call_plain("b200_ep_ipc_export", ctypes.byref(_lib.to_aiter(self.recv)), handle, ctypes.byref(offset))
+        err = None
+        try:
+            _lib.call_plain("b200_ep_ipc_export", ctypes.byref(_lib.to_aiter(self.arena)), handle, ctypes.byref(offset))
+        except RuntimeError as e:
+            err = str(e)
         exported = [None] * world
-        dist.all_gather_object(exported, (handle.raw, int(offset.value)), group=group)
-        # every peer's buffer is mapped with THIS rank's device current: a mapping belongs to the device it was
-        # opened under, and the push kernel of this rank is what stores through it
+        dist.all_gather_object(exported, (handle.raw, int(offset.value), err), group=group)
+        # every peer's arena is mapped with THIS rank's device current: a mapping belongs to the device it was
+        # opened under, and the kernels of this rank are what store through it
         self.mapped = []
-        addrs = []
-        for r in range(world):
-            if r == rank:
-                addrs.append(self.recv.data_ptr())
-                continue
-            base = ctypes.c_int64(0)
-            _lib.call_plain("b200_ep_ipc_open", ctypes.create_string_buffer(exported[r][0], 64), int(device.index),
-                            ctypes.byref(base))
-            self.mapped.append(int(base.value))
-            addrs.append(int(base.value) + exported[r][1])
-        self.ptrs = torch.tensor(addrs, dtype=torch.int64, device=device)
-        dist.barrier(group=group)       # nobody pushes into a buffer that is not mapped everywhere yet
+        bases = []
+        if all(e[2] is None for e in exported):
+            try:
+                for r in range(world):
+                    if r == rank:
+                        bases.append(self.arena.data_ptr())
+                        continue
+                    base = ctypes.c_int64(0)
+                    _lib.call_plain("b200_ep_ipc_open", ctypes.create_string_buffer(exported[r][0], 64),
+                                    int(device.index), ctypes.byref(base))
+                    self.mapped.append(int(base.value))
+                    bases.append(int(base.value) + exported[r][1])
+            except RuntimeError as e:
+                err = str(e)
+        else:
+            err = next(e[2] for e in exported if e[2] is not None)
+        ok = torch.tensor([0 if err else 1], dtype=torch.int32, device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)
+        if int(ok.item()) == 0:
+            self.close()
+            raise RuntimeError(f"peer-memory exchange unavailable: {err or 'mapping failed on another rank'}")
+        table = lambda off: torch.tensor([b + off for b in bases], dtype=torch.int64, device=device)
+        self.ptrs_recv, self.ptrs_a1, self.ptrs_a1_scale = table(off_recv), table(off_a1), table(off_a1s)
 
     def close(self):
         for base in self.mapped:
@@ -109,14 +138,13 @@ class PeerExchange:
         return cls._cache[key]
 
 
-def _p2p_combine(partial, ids, num_experts, group, dtype, timers):
+def _p2p_combine(ex, partial, ids, num_experts, group, dtype, timers):
     """partial [M, H] fp32 of this rank -> out [M/G, H]: push, barrier, combine."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     M, H = partial.shape
     m_local = M // world
-    ex = PeerExchange.get(group, m_local, H, partial.device)
     epr = num_experts // world
-    _lib.call("b200_ep_push_partials", partial, ids, ex.ptrs, rank, world, epr, device=partial.device)
+    _lib.call("b200_ep_push_partials", partial, ids, ex.ptrs_recv, rank, world, epr, device=partial.device)
     _mark(timers, "ep_barrier")
     dist.all_reduce(ex.flag, group=group)   # passes only after every rank's push kernel has completed
     _mark(timers, "ep_combine")
@@ -145,8 +173,25 @@ def ep_fused_moe(x_local, w1_local, w2_local, topk_weight_local, topk_ids_local,
     _mark(timers, "ep_quant")
     a1_l, a1s_l = quant(x_local)
     _mark(timers, "ep_all_gather")
+    ex = None
+    if exchange not in ("nccl", "p2p"):
+        raise ValueError(f"exchange must be 'nccl' or 'p2p', got {exchange!r}")
     if world == 1:
         a1, a1s, ids, wts = a1_l, a1s_l, topk_ids_local, topk_weight_local
+    elif exchange == "p2p":
+        # token rows go only to the ranks that hold one of their experts (peer stores); the routing table of all
+        # tokens is small and is all-gathered - a collective issued after the dispatch kernel, so passing it also
+        # means every rank's rows have landed
+        ex = PeerExchange.get(group, m_local, H, dev)
+        ids_l = topk_ids_local.contiguous()
+        _lib.call("b200_ep_dispatch", a1_l, a1s_l.view(m_local, -1), ids_l, ex.ptrs_a1, ex.ptrs_a1_scale, rank, world,
+                  num_experts // world, device=dev)
+        side_l = torch.cat([ids_l.view(torch.int32), topk_weight_local.contiguous().view(torch.int32)], dim=1)
+        side = torch.empty((world * m_local, side_l.shape[1]), dtype=torch.int32, device=dev)
+        dist.all_gather_into_tensor(side, side_l, group=group)
+        a1, a1s = ex.a1, ex.a1_scale
+        ids = side[:, :topk].contiguous()
+        wts = side[:, topk:].contiguous().view(torch.float32)
     else:
         # two collectives: the codes, and one int32 side buffer per row with scales, ids and weights
         kb = a1s_l.shape[1]
@@ -163,6 +208,8 @@ def ep_fused_moe(x_local, w1_local, w2_local, topk_weight_local, topk_ids_local,
     mask = expert_mask_for_rank(num_experts, rank, world, device=dev)
     if overlap_chunks is None:
         overlap_chunks = 1   # measured on 8 x B200: the ranged reduce-scatters gain nothing over one call
+    if overlap_chunks > 1 and ex is not None:
+        raise ValueError("overlap_chunks > 1 belongs to the NCCL exchange")
     if overlap_chunks > 1:
         # column ranges: the reduce-scatter of range c runs (on NCCL's stream) beside stage 2 of range c+1
         hc = H // overlap_chunks
@@ -192,13 +239,11 @@ def ep_fused_moe(x_local, w1_local, w2_local, topk_weight_local, topk_ids_local,
         timers.pop()   # the local layer's own "end" mark: the next mark takes its place
     else:
         partial = local_layer(a1, a1s, w1_local, w2_local, wts, ids, mask, w1_scale_local, w2_scale_local)
-    if exchange == "p2p" and world > 1:
+    if ex is not None:
         _mark(timers, "ep_push")
-        out = _p2p_combine(partial, ids, num_experts, group, dtype, timers)
+        out = _p2p_combine(ex, partial, ids, num_experts, group, dtype, timers)
         _mark(timers, "end")
         return out
-    if exchange not in ("nccl", "p2p"):
-        raise ValueError(f"exchange must be 'nccl' or 'p2p', got {exchange!r}")
     _mark(timers, "ep_reduce_scatter")
     if world == 1:
         mine = partial

@@ -288,8 +288,9 @@ def main():
     ap.add_argument("--tokens", type=int, default=M_PREFILL, help="override M (profiling a small case)")
     ap.add_argument("--experts", type=int, default=E, help="override E (profiling a small case)")
     ap.add_argument("--skip-decode", action="store_true")
-    ap.add_argument("--ep-exchange", default="nccl", choices=["nccl", "p2p"],
-                    help="N>1: fp32 reduce-scatter of the partial sums, or peer-memory push + combine")
+    ap.add_argument("--ep-exchange", default="auto", choices=["auto", "nccl", "p2p"],
+                    help="N>1: NCCL all-gather + fp32 reduce-scatter, or dispatch/combine over peer memory; auto = "
+                         "peer memory if every rank can map its peers' buffers, else NCCL")
     ap.add_argument("--cuda-profiler-range", action="store_true",
                     help="bracket the device-timed steps with cudaProfilerStart/Stop (ncu --profile-from-start off)")
     args = ap.parse_args()
@@ -332,6 +333,14 @@ def main():
     hout2 = [hout, torch.empty((m_local, H), dtype=torch.bfloat16).pin_memory()]
     dx, dtw, dti = hx.to(dev), htw.to(dev), hti.to(dev)
 
+    exchange = args.ep_exchange
+    if world > 1 and exchange == "auto":
+        try:
+            ep.PeerExchange.get(None, m_local, H, dev)   # collective; fails on all ranks or on none
+            exchange = "p2p"
+        except RuntimeError as e:
+            print(f"[bench] peer-memory exchange not available ({e}); using NCCL", file=sys.stderr)
+            exchange = "nccl"
     if world == 1:
         def step_dev():
             return aiter_b200.fused_moe(dx, w1_q, w2_q, dtw, dti, quant_type=QT.per_1x128,
@@ -341,10 +350,10 @@ def main():
             return aiter_b200.fused_moe(a, w1_q, w2_q, b, c, quant_type=QT.per_1x128, w1_scale=w1_s, w2_scale=w2_s)
     else:
         def step_dev():
-            return ep.ep_fused_moe(dx, w1_q, w2_q, dtw, dti, w1_s, w2_s, E, exchange=args.ep_exchange)
+            return ep.ep_fused_moe(dx, w1_q, w2_q, dtw, dti, w1_s, w2_s, E, exchange=exchange)
 
         def layer(a, b, c):
-            return ep.ep_fused_moe(a, w1_q, w2_q, b, c, w1_s, w2_s, E, exchange=args.ep_exchange)
+            return ep.ep_fused_moe(a, w1_q, w2_q, b, c, w1_s, w2_s, E, exchange=exchange)
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -375,7 +384,7 @@ def main():
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate, bf16 in/out)", "data": "synthetic",
         "config": {"workload": WORKLOAD, "tokens": M_PREFILL, "model_dim": H, "inter_dim": I, "experts": E,
-                   "topk": TOPK, "parallelism": f"ep{world}", "l2_policy": "inputs larger than L2 (11.3 GB of weights per step)"},
+                   "topk": TOPK, "parallelism": f"ep{world}" + (f" ({exchange} exchange)" if world > 1 else ""), "l2_policy": "inputs larger than L2 (11.3 GB of weights per step)"},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": int(hx.numel() * 2 + htw.numel() * 4 + hti.numel() * 4) * world,
                 "d2h_bytes_per_step": int(hout.numel() * 2) * world,
@@ -451,7 +460,7 @@ def main():
         accb = {}
         for _ in range(5):
             timers = []
-            ep.ep_fused_moe(dx, w1_q, w2_q, dtw, dti, w1_s, w2_s, E, timers=timers, exchange=args.ep_exchange)
+            ep.ep_fused_moe(dx, w1_q, w2_q, dtw, dti, w1_s, w2_s, E, timers=timers, exchange=exchange)
             sync()
             for (n0, e0), (_n1, e1) in zip(timers[:-1], timers[1:]):
                 accb.setdefault(n0, []).append(e0.elapsed_time(e1))

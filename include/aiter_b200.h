@@ -173,6 +173,12 @@ int b200_moe_finalize(aiter_tensor_t* out, const aiter_tensor_t* acc, void* stre
  * partial sums. The reference's counterparts are MoRI's combine and the stage-2 scatter epilogue into a
  * peer-memory arena (`Stage2ScatterContext`, aiter/fused_moe.py:536-575; oracle
  * op_tests/multigpu_tests/test_dispatch_combine.py:18-72).
+ *   b200_ep_dispatch: the quantised row of every local token (a1 [m_local,H] fp8, a1_scale [m_local,H/128] fp32) is
+ *     stored at the token's global row (rank*m_local + row) of the a1 / a1_scale buffers ([M,H], [M,H/128]) of every
+ *     rank that holds one of the experts in topk_ids[row,:] (i32 [m_local,topk], GLOBAL ids); peer_a1 and
+ *     peer_a1_scale are i64 [world] device arrays with those buffers' addresses as mapped in this process (the
+ *     rank's own buffers included). Takes the place of the all-gather of the tokens; rows a rank has no route
+ *     for are not sent (and never read by its stage 1).
  *   b200_ep_push_partials: rank `rank` copies acc[t,:] (fp32 [M,H], M = world * m_local) of every token t owned
  *     by another rank o for which topk_ids[t,:] (i32 [M,topk], GLOBAL expert ids) names one of its experts
  *     (id / experts_per_rank == rank) into recv_o[rank, t - o*m_local, :]; peer_recv is an i64 [world] device
@@ -185,6 +191,9 @@ int b200_moe_finalize(aiter_tensor_t* out, const aiter_tensor_t* acc, void* stre
  *     process for kernels of `device` (the mapping belongs to the device that is current while it is opened, so
  *     every rank opens its peers' handles under its own device) and returns the base address; close unmaps it.
  * No device-side waiting between ranks; rows that were not pushed are never read. */
+int b200_ep_dispatch(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale, const aiter_tensor_t* topk_ids,
+                     const aiter_tensor_t* peer_a1, const aiter_tensor_t* peer_a1_scale, int rank, int world,
+                     int experts_per_rank, void* stream);
 int b200_ep_push_partials(const aiter_tensor_t* acc, const aiter_tensor_t* topk_ids, const aiter_tensor_t* peer_recv,
                           int rank, int world, int experts_per_rank, void* stream);
 int b200_ep_combine(aiter_tensor_t* out, const aiter_tensor_t* acc, const aiter_tensor_t* recv,
