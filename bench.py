@@ -8,8 +8,8 @@ One "step" is one pass of the layer over one batch of synthetic tokens (seeded N
 N(0,1/sqrt(K)) weights quantised to e4m3 per 128x128 block, DeepSeek-V3 grouped top-8 routing).
 Headline workload: M=8192 tokens, H=7168, I=2048, E=256, topk=8 (prefill); the M=64 decode case is
 measured in the same run and reported under "decode".  With N GPUs the experts are sharded
-(expert parallelism: token all-gather, local layer, fp32 reduce-scatter) and the total work stays
-fixed, so scaling is "strong".  Rank 0 prints ONE JSON line.
+(expert parallelism: token dispatch, local layer, combine of the fp32 partial sums; over peer memory or
+NCCL) and the total work stays fixed, so scaling is "strong".  Rank 0 prints ONE JSON line.
 
 `--impl reference` times the CPU oracle (the reference's torch arithmetic restated per expert) on
 the host cores over a bounded sample of the same workload.

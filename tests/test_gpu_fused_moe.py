@@ -178,6 +178,23 @@ def test_every_route_to_one_expert(M):
     assert_parity(run(c), ref, f"one expert, M={M}")
 
 
+def test_shared_expert_folded_as_extra_expert():
+    """How serving stacks run DeepSeek-V3's shared expert through this op: it is appended as expert id E and every
+    token gets one more route to it with weight 1 (the E=257, topk=9 rows of the reference's tuned configurations,
+    aiter/configs/model_configs/a8w8_blockscale_tuned_fmoe_ds_v3.csv). Nothing in the layer is special-cased for it."""
+    M, H, I, E, topk = 96, 512, 256, 8, 2
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn((M, H), generator=g).to(torch.bfloat16)
+    w1_q, w1_s = inputs.make_weights(E + 1, 2 * I, H, seed=21)
+    w2_q, w2_s = inputs.make_weights(E + 1, H, I, seed=22)
+    tw, ti = inputs.make_routing("softmax", M, E, topk, seed=3)
+    ti = torch.cat([ti, torch.full((M, 1), E, dtype=torch.int32)], dim=1)
+    tw = torch.cat([tw, torch.ones((M, 1), dtype=torch.float32)], dim=1)
+    ref = moe_oracle.fused_moe_ref(x, w1_q, w1_s, w2_q, w2_s, tw, ti)
+    c = to_dev(dict(x=x, w1_q=w1_q, w1_scale=w1_s, w2_q=w2_q, w2_scale=w2_s, topk_weight=tw, topk_ids=ti))
+    assert_parity(run(c), ref, "shared expert as expert E")
+
+
 def test_dsv3_decode_full_size():
     """cfg1: M=64, H=7168, I=2048, E=256, topk=8 with DeepSeek-V3 grouped routing. The weights are
     drawn on the GPU (11.3 GB); the oracle runs per expert on the host."""
