@@ -1,0 +1,92 @@
+"""The peer-memory exchange kernels (dispatch, push, combine) with all ranks emulated on ONE GPU.
+
+Every "rank" gets its own arena on the same device and the address tables point at those arenas, so the
+kernels run exactly as they do across GPUs (same index arithmetic, same rank/world arguments) while the
+launches of the ranks follow one another on one stream. Buffers start out filled with NaN patterns: a row
+that was not sent must never be read."""
+
+import pytest
+import torch
+
+import aiter_b200
+from aiter_b200 import _lib, ep
+from aiter_b200.fused_moe import fused_moe_stages, per_group_quant_hip
+from oracle import inputs, moe_oracle
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.mark.parametrize("world,routing", [(2, "softmax"), (4, "zipf")])
+def test_dispatch_push_combine_emulated_ranks(world, routing):
+    M, H, I, E, topk = 256, 512, 256, 8, 2
+    g = torch.Generator().manual_seed(world)
+    x = torch.randn((M, H), generator=g).to(torch.bfloat16)
+    w1_q, w1_s = inputs.make_weights(E, 2 * I, H, seed=31)
+    w2_q, w2_s = inputs.make_weights(E, H, I, seed=32)
+    tw, ti = inputs.make_routing(routing, M, E, topk, seed=5)
+    ref = moe_oracle.fused_moe_ref(x, w1_q, w1_s, w2_q, w2_s, tw, ti)
+
+    dev = torch.device(DEV)
+    d = lambda t: t.to(dev)
+    x, w1_q, w1_s, w2_q, w2_s, tw, ti = map(d, (x, w1_q, w1_s, w2_q, w2_s, tw, ti))
+    m_local, epr, kb = M // world, E // world, H // 128
+    nan_bytes = lambda shape: torch.full(shape, 0x7F, dtype=torch.uint8, device=dev)   # e4m3 NaN codes
+    a1_all = [nan_bytes((M, H)).view(torch.float8_e4m3fn) for _ in range(world)]
+    a1s_all = [torch.full((M, kb), float("nan"), device=dev) for _ in range(world)]
+    recv = [torch.full((world, m_local, H), float("nan"), device=dev) for _ in range(world)]
+    table = lambda bufs: torch.tensor([b.data_ptr() for b in bufs], dtype=torch.int64, device=dev)
+    p_a1, p_a1s, p_recv = table(a1_all), table(a1s_all), table(recv)
+
+    # 1. dispatch: every rank stores its rows where they are needed
+    for r in range(world):
+        rows = slice(r * m_local, (r + 1) * m_local)
+        q, s = per_group_quant_hip(x[rows])
+        _lib.call("b200_ep_dispatch", q, s, ti[rows].contiguous(), p_a1, p_a1s, r, world, epr, device=dev)
+    # rows arrived exactly where a route exists
+    owner_of_expert = ti // epr
+    q_all, s_all = per_group_quant_hip(x)
+    for r in range(world):
+        need = (owner_of_expert == r).any(dim=1)
+        got = ~torch.isnan(a1s_all[r]).any(dim=1)
+        assert torch.equal(need, got), f"rank {r}: dispatched rows differ from the routing"
+        assert torch.equal(a1_all[r].view(torch.uint8)[need], q_all.view(torch.uint8)[need])
+        assert torch.equal(a1s_all[r][need], s_all[need])
+
+    # 2. local layers (non-local routes dropped by the sort), 3. push, 4. combine
+    partial = []
+    for r in range(world):
+        sl = slice(r * epr, (r + 1) * epr)
+        mask = ep.expert_mask_for_rank(E, r, world, device=dev)
+        partial.append(fused_moe_stages(a1_all[r], w1_q[sl].contiguous(), w2_q[sl].contiguous(), tw, ti, mask,
+                                        w1_s[sl].contiguous(), w2_s[sl].contiguous(), a1s_all[r], None, None))
+    for r in range(world):
+        _lib.call("b200_ep_push_partials", partial[r], ti, p_recv, r, world, epr, device=dev)
+    outs = []
+    for r in range(world):
+        out = torch.empty((m_local, H), dtype=torch.bfloat16, device=dev)
+        _lib.call("b200_ep_combine", out, partial[r], recv[r], ti, r, world, epr, device=dev)
+        outs.append(out)
+    torch.cuda.synchronize()
+    aiter_b200.check_device_status()
+    out = torch.cat(outs, dim=0).cpu()
+    # against the same layer on one rank: same kernels, same per-route sums, only the order of the final fp32
+    # additions differs (rank order here, arrival order of the reductions there) -> isolated one-ulp flips at most
+    single = aiter_b200.fused_moe(x, w1_q, w2_q, tw, ti, quant_type=aiter_b200.QuantType.per_1x128,
+                                  w1_scale=w1_s, w2_scale=w2_s).cpu()
+    s1 = moe_oracle.error_stats(out, single)
+    print(f"emulated ep{world} vs one rank: {s1}")
+    assert not s1["has_nan"] and s1["n_diff"] == s1["n_one_ulp"] and s1["n_diff"] <= 2e-3 * s1["numel"], s1
+    # against the oracle: the bars of the layer tests (small K: a flipped e4m3 code of stage 1 shows as 2-3 ulps)
+    s = moe_oracle.error_stats(out, ref)
+    print(f"emulated ep{world} vs oracle: {s}")
+    assert s["frac_within"] >= 0.995 and s["max_abs_over_rms"] <= 0.04, s
+    # rows a rank did not produce were not pushed: their slots still hold the NaN fill
+    for o in range(world):
+        rows = slice(o * m_local, (o + 1) * m_local)
+        for r in range(world):
+            if r == o:
+                continue
+            touched = (owner_of_expert[rows] == r).any(dim=1)
+            arrived = ~torch.isnan(recv[o][r]).any(dim=1)
+            assert torch.equal(touched, arrived), f"rows pushed from rank {r} to rank {o} differ from the routing"
