@@ -84,11 +84,6 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
                  : "memory");
 }
-// 4-byte copy (src_bytes = 0 writes a zero).
-__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src, uint32_t src_bytes) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
-                 : "memory");
-}
 // mbarrier arrival that fires once every cp.async this thread has issued so far has landed;
 // it counts as one of the barrier's expected arrivals.
 __device__ __forceinline__ void cp_async_mbar_arrive(uint32_t bar) {
@@ -170,25 +165,10 @@ __host__ __device__ constexpr uint32_t make_idesc_e4m3_f32(int m, int n) {
     return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-// 32 consecutive fp32 columns of this thread's TMEM lane, loaded AND waited for in one asm
+// 16 consecutive fp32 columns of this thread's TMEM lane, loaded AND waited for in one asm
 // statement: the registers are valid when the statement ends, so the compiler cannot schedule a
-// consumer between the asynchronous load and its tcgen05.wait::ld.
-__device__ __forceinline__ void tmem_ld_x32_sync(uint32_t taddr, uint32_t* r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
-        "tcgen05.wait::ld.sync.aligned;"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-          "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
-          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
-          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-
-// 16-column variant of the above (half the temporaries: the promotion loop lives at the register limit).
+// consumer between the asynchronous load and its tcgen05.wait::ld. (16, not 32 columns per load: the
+// promotion loop lives at the register limit.)
 __device__ __forceinline__ void tmem_ld_x16_sync(uint32_t taddr, uint32_t* r) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -205,13 +185,6 @@ __device__ __forceinline__ float rcp_approx(float x) {
     float y;
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
-}
-
-// Vector fp32 reduction into global memory (one 16-byte L2 atomic).
-__device__ __forceinline__ void red_add_v4(float* dst, float a, float b, float c, float d) {
-    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "f"(a), "f"(b), "f"(c),
-                 "f"(d)
-                 : "memory");
 }
 
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, float a, float b, float c, float d) {
