@@ -93,21 +93,56 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------ inputs
+def quantise_weights(E_, N, K, seed, device):
+    """[E_, N, K] ~ N(0, 1/sqrt(K)) drawn on `device` one expert at a time and quantised to e4m3 per 128x128 block
+    with scale = amax/448 (0 -> 1): the weight format of the reference's tests (op_tests/test_moe_2stage.py:184-208)."""
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    q = torch.empty((E_, N, K), dtype=torch.float8_e4m3fn, device=device)
+    s = torch.empty((E_, N // 128, K // 128), dtype=torch.float32, device=device)
+    std = 1.0 / (K ** 0.5)
+    for e in range(E_):
+        w = torch.randn((N, K), generator=g, dtype=torch.float32, device=device) * std
+        blocks = w.view(N // 128, 128, K // 128, 128)
+        amax = blocks.abs().amax(dim=(1, 3), keepdim=True)
+        scale = amax / 448.0
+        scale[scale == 0] = 1.0
+        q[e] = (blocks / scale).view(N, K).to(torch.float8_e4m3fn)
+        s[e] = scale.view(N // 128, K // 128)
+    return q, s
+
+
 def make_layer(device, rank, world, seed=0):
-    """This rank's expert slice (weights drawn on the device) and the full routing."""
-    from oracle import inputs
+    """This rank's expert slice (weights drawn and quantised on the device)."""
     e_local = E // world
-    w1_q, w1_s = inputs.make_weights(e_local, 2 * I, H, seed + 1 + 1000 * rank, device)
-    w2_q, w2_s = inputs.make_weights(e_local, H, I, seed + 2 + 1000 * rank, device)
+    w1_q, w1_s = quantise_weights(e_local, 2 * I, H, seed + 1 + 1000 * rank, device)
+    w2_q, w2_s = quantise_weights(e_local, H, I, seed + 2 + 1000 * rank, device)
     return w1_q, w1_s, w2_q, w2_s
 
 
-def make_tokens(M, seed=0):
-    from oracle import inputs
+def router_inputs(M, seed=0):
+    """Seeded activations, router logits ~ N(0,1) and correction bias ~ N(0, 0.1) (host generator)."""
     g = torch.Generator().manual_seed(seed)
     x = torch.randn((M, H), generator=g, dtype=torch.float32).to(torch.bfloat16)
-    tw, ti = inputs.make_routing("dsv3", M, E, TOPK, seed)
-    return x, tw, ti
+    g = torch.Generator().manual_seed(seed + 3)
+    logits = torch.randn((M, E), generator=g, dtype=torch.float32)
+    bias = torch.randn((E,), generator=g, dtype=torch.float32) * 0.1
+    return x, logits, bias
+
+
+def make_tokens(M, seed=0, device=None):
+    """x [M,H] bf16 and DeepSeek-V3 routing (8 groups, top-4 groups, top-8 experts, renormalised, x2.5): computed by
+    this library's own router kernel on `device`; on the host (the CPU legs, device=None) by the oracle's router."""
+    x, logits, bias = router_inputs(M, seed)
+    if device is None:
+        from oracle import moe_oracle
+        tw, ti = moe_oracle.biased_grouped_topk_ref(logits, bias, TOPK, True, 8, 4, routed_scaling_factor=2.5)
+        return x, tw, ti
+    import aiter_b200
+    tw = torch.empty((M, TOPK), dtype=torch.float32, device=device)
+    ti = torch.empty((M, TOPK), dtype=torch.int32, device=device)
+    aiter_b200.biased_grouped_topk(logits.to(device), bias.to(device), tw, ti, 8, 4, True, 2.5)
+    return x, tw.cpu(), ti.cpu()
 
 
 # ------------------------------------------------------------------------------------------ CPU arm
@@ -124,12 +159,11 @@ def cpu_sample_step(x, tw, ti, w1_q, w1_s, w2_q, w2_s, n_exp):
 
 
 def cpu_baseline(n_exp=8, steps=1, warmup=0, seed=0):
-    from oracle import inputs
     cores = len(os.sched_getaffinity(0))
     torch.set_num_threads(cores)
     x, tw, ti = make_tokens(M_PREFILL, seed)
-    w1_q, w1_s = inputs.make_weights(n_exp, 2 * I, H, seed + 1)
-    w2_q, w2_s = inputs.make_weights(n_exp, H, I, seed + 2)
+    w1_q, w1_s = quantise_weights(n_exp, 2 * I, H, seed + 1, "cpu")
+    w2_q, w2_s = quantise_weights(n_exp, H, I, seed + 2, "cpu")
     times, fl = [], 0.0
     for i in range(warmup + steps):
         dt, fl = cpu_sample_step(x, tw, ti, w1_q, w1_s, w2_q, w2_s, n_exp)
@@ -324,7 +358,7 @@ def main():
             torch.cuda.synchronize()
 
     w1_q, w1_s, w2_q, w2_s = make_layer(dev, rank, world)
-    x, tw, ti = make_tokens(M_PREFILL)
+    x, tw, ti = make_tokens(M_PREFILL, device=dev)
     m_local = M_PREFILL // world
     rows = slice(rank * m_local, (rank + 1) * m_local)
     # pinned host copies of this rank's step inputs, and a pinned landing buffer for its output
@@ -422,7 +456,7 @@ def main():
             line["roofline"]["frac_of_library_fp8_gemm"] = s1 / lib
     if world == 1 and not args.skip_decode:
         # ---- decode case (M=64): HBM-bound weight streaming
-        xd, twd, tid = make_tokens(M_DECODE, seed=1)
+        xd, twd, tid = make_tokens(M_DECODE, seed=1, device=dev)
         dxd, dtwd, dtid = xd.to(dev), twd.to(dev), tid.to(dev)
         n_act = int(torch.unique(tid).numel())
 
@@ -465,6 +499,29 @@ def main():
             for (n0, e0), (_n1, e1) in zip(timers[:-1], timers[1:]):
                 accb.setdefault(n0, []).append(e0.elapsed_time(e1))
         line["ep_breakdown_ms_rank0"] = {k: round(sum(v) / len(v), 4) for k, v in accb.items()}
+        line["gpu_launches"] = ((3 + 4) + (3 if exchange == "p2p" else 0)) * args.steps * 2
+        # Roofline of the sharded layer: the slower of (this rank's share of the flops at the FP8 peak) and (the bytes
+        # that must cross NVLink per rank at the measured 770 GB/s per direction); achieved = the step time.
+        epr = E // world
+        touched = torch.zeros((M_PREFILL, world), dtype=torch.bool)
+        touched.scatter_(1, (ti // epr).long(), True)                       # [token, rank]: a route on that rank
+        owner = torch.arange(M_PREFILL) // m_local
+        remote = touched.clone()
+        remote[torch.arange(M_PREFILL), owner] = False                      # rows that leave the owning rank
+        kb = H // 128
+        if exchange == "p2p":
+            disp = remote.sum(1)[owner == 0].sum().item() * (H + kb * 4)    # rank 0 sends its rows to the ranks that need them
+            comb = remote[:, 0].sum().item() * H * 4                        # rank 0 pushes the partial rows it produced
+        else:
+            disp = (world - 1) * m_local * (H + kb * 4 + 8 * TOPK)          # all-gather: every rank receives the others' rows
+            comb = (world - 1) * m_local * H * 4                            # reduce-scatter of fp32 partials
+        t_flops = flops(M_PREFILL) / world / (fp8_peak * 1e12) * 1e3
+        t_link = (disp + comb) / 770e9 * 1e3
+        line["roofline"] = {"bound": "tensor" if t_flops >= t_link else "nvlink", "achieved": value / world,
+                            "peak": fp8_peak, "unit": "TFLOP/s per GPU", "frac": max(t_flops, t_link) / ms_step,
+                            "traffic": None, "nvlink_bytes_rank0": int(disp + comb),
+                            "target_ms": {"flops_at_fp8_peak": t_flops, "nvlink_at_770GBs": t_link},
+                            "peak_source": f"2 x bf16_tflops of {pk['source']}; NVLink: 770 GB/s per direction measured on this pool"}
 
     if rank == 0:
         emit(line)

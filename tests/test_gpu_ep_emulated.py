@@ -17,9 +17,12 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-@pytest.mark.parametrize("world,routing", [(2, "softmax"), (4, "zipf")])
-def test_dispatch_push_combine_emulated_ranks(world, routing):
-    M, H, I, E, topk = 256, 512, 256, 8, 2
+@pytest.mark.parametrize("world,routing,E,topk", [
+    (2, "softmax", 8, 2), (4, "zipf", 8, 2),
+    (8, "dsv3", 64, 8),   # the benchmark's structure in small: 8 groups = 8 ranks, a token's routes on <= 4 of them
+])
+def test_dispatch_push_combine_emulated_ranks(world, routing, E, topk):
+    M, H, I = 256, 512, 256
     g = torch.Generator().manual_seed(world)
     x = torch.randn((M, H), generator=g).to(torch.bfloat16)
     w1_q, w1_s = inputs.make_weights(E, 2 * I, H, seed=31)
