@@ -34,13 +34,20 @@ from . import _lib, dtypes
 from .fused_moe import _mark, fused_moe_stages, per_group_quant_hip
 
 
+_MASKS: dict = {}
+
+
 def expert_mask_for_rank(num_experts: int, rank: int, world: int, device=None) -> torch.Tensor:
     """[global_E] int32, 1 for the contiguous slice of experts owned by ``rank``."""
     if num_experts % world != 0:
         raise ValueError(f"num_experts ({num_experts}) must be divisible by the EP world size ({world})")
-    per = num_experts // world
-    mask = torch.zeros(num_experts, dtype=torch.int32, device=device)
-    mask[rank * per:(rank + 1) * per] = 1
+    key = (num_experts, rank, world, str(device))
+    mask = _MASKS.get(key)
+    if mask is None:   # built once per layout: two launches less on every layer call
+        per = num_experts // world
+        mask = torch.zeros(num_experts, dtype=torch.int32, device=device)
+        mask[rank * per:(rank + 1) * per] = 1
+        _MASKS[key] = mask
     return mask
 
 
