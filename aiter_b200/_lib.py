@@ -38,22 +38,22 @@ _SIGNATURES = {
     "aiter_ctypes_abi_version": (ctypes.c_int, []),
     "aiter_get_last_error": (ctypes.c_char_p, []),
     "aiter_clear_last_error": (None, []),
-    "b200_moe_sorting_get_workspace_size": (ctypes.c_int64, [ctypes.c_int] * 3),
+    "b200_moe_sorting_get_workspace_size": (ctypes.c_int64, [ctypes.c_int] * 4),
     "b200_moe_sorting_fwd": (ctypes.c_int, [_T] * 7 + [ctypes.c_int, ctypes.c_int, _T, _T, _T,
-                                                ctypes.c_int, _T, ctypes.c_void_p]),
+                                                ctypes.c_int, _T, _T, _T, ctypes.c_void_p]),
     "b200_moe_sorting_fwd_noalloc": (ctypes.c_int, [_T] * 7 + [ctypes.c_int, ctypes.c_int, _T, _T, _T,
                                                         ctypes.c_void_p]),
-    "b200_moe_quant_1x128": (ctypes.c_int, [_T] * 3 + [ctypes.c_void_p]),
-    "b200_moe_quant_per_token": (ctypes.c_int, [_T] * 4 + [ctypes.c_void_p]),
+    "b200_moe_quant_1x128": (ctypes.c_int, [_T] * 4 + [ctypes.c_int, ctypes.c_int, ctypes.c_void_p]),
+    "b200_moe_quant_per_token": (ctypes.c_int, [_T] * 4 + [ctypes.c_int, ctypes.c_void_p]),
     "b200_moe_stage1": (ctypes.c_int, [_T] * 10 + [ctypes.c_int, _T, ctypes.c_int, ctypes.c_void_p]),
     "b200_moe_stage2": (ctypes.c_int, [_T] * 10 + [ctypes.c_int] * 5 + [ctypes.c_void_p]),
     "b200_biased_grouped_topk": (ctypes.c_int, [_T] * 4 + [ctypes.c_int] * 3 + [ctypes.c_float, ctypes.c_void_p]),
     "b200_topk_softmax": (ctypes.c_int, [_T] * 4 + [ctypes.c_int, ctypes.c_void_p]),
     "b200_moe_finalize": (ctypes.c_int, [_T] * 2 + [ctypes.c_void_p]),
     "b200_moe_quant_per_tensor": (ctypes.c_int, [_T] * 6 + [ctypes.c_void_p]),
-    "b200_ep_dispatch": (ctypes.c_int, [_T] * 5 + [ctypes.c_int] * 3 + [ctypes.c_void_p]),
-    "b200_ep_push_partials": (ctypes.c_int, [_T] * 3 + [ctypes.c_int] * 3 + [ctypes.c_void_p]),
-    "b200_ep_combine": (ctypes.c_int, [_T] * 4 + [ctypes.c_int] * 3 + [ctypes.c_void_p]),
+    "b200_ep_dispatch": (ctypes.c_int, [_T] * 5 + [ctypes.c_int] * 3 + [_T, ctypes.c_void_p]),
+    "b200_ep_push_partials": (ctypes.c_int, [_T] * 3 + [ctypes.c_int] * 3 + [_T, ctypes.c_void_p]),
+    "b200_ep_combine": (ctypes.c_int, [_T] * 4 + [ctypes.c_int] * 3 + [_T, ctypes.c_void_p]),
     "b200_ep_ipc_export": (ctypes.c_int, [_T, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64)]),
     "b200_ep_ipc_open": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_int64)]),
     "b200_ep_ipc_close": (ctypes.c_int, [ctypes.c_int64, ctypes.c_int]),
@@ -75,7 +75,7 @@ def lib():
             fn = getattr(handle, name)  # AttributeError if the symbol is not exported
             fn.restype = res
             fn.argtypes = args
-        if handle.aiter_ctypes_abi_version() != 2:
+        if handle.aiter_ctypes_abi_version() != 3:
             raise RuntimeError("libaiter_b200.so: unexpected C-ABI version")
         _lib = handle
     return _lib

@@ -21,8 +21,8 @@ void launch_moe_sorting(const aiter_tensor_t*, const aiter_tensor_t*, aiter_tens
 void launch_moe_sorting_noalloc(const aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*,
                                 aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*, int, int, const aiter_tensor_t*,
                                 const aiter_tensor_t*, aiter_tensor_t*, cudaStream_t);
-void launch_quant_1x128(aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*, cudaStream_t);
-void launch_quant_per_token(aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*, const aiter_tensor_t*, cudaStream_t);
+void launch_quant_1x128(aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*, const aiter_tensor_t*, int, int, cudaStream_t);
+void launch_quant_per_token(aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*, const aiter_tensor_t*, int, cudaStream_t);
 void launch_quant_per_tensor(aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*,
                              const aiter_tensor_t*, cudaStream_t);
 void launch_moe_stage1(const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*,
@@ -35,11 +35,12 @@ void launch_moe_stage2(const aiter_tensor_t*, const aiter_tensor_t*, const aiter
 void launch_biased_grouped_topk(const aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*, int, int,
                                 int, float, cudaStream_t);
 void launch_topk_softmax(aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*, const aiter_tensor_t*, int, cudaStream_t);
-void launch_ep_push(const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, int, int, int, cudaStream_t);
+void launch_ep_push(const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, int, int, int, const aiter_tensor_t*,
+                    cudaStream_t);
 void launch_ep_combine(aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, int, int, int,
-                       cudaStream_t);
+                       const aiter_tensor_t*, cudaStream_t);
 void launch_ep_dispatch(const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*,
-                        const aiter_tensor_t*, int, int, int, cudaStream_t);
+                        const aiter_tensor_t*, int, int, int, const aiter_tensor_t*, cudaStream_t);
 void ipc_export(const aiter_tensor_t*, void*, int64_t*);
 void ipc_open(const void*, int, int64_t*);
 void ipc_close(int64_t, int);
@@ -95,13 +96,14 @@ using namespace b200;
 
 extern "C" {
 
-B200_EXPORT int aiter_ctypes_abi_version(void) { return 2; }
+B200_EXPORT int aiter_ctypes_abi_version(void) { return 3; }
 
 B200_EXPORT const char* aiter_get_last_error(void) { return last_error().empty() ? nullptr : last_error().c_str(); }
 
 B200_EXPORT void aiter_clear_last_error(void) { last_error().clear(); }
 
-B200_EXPORT int64_t b200_moe_sorting_get_workspace_size(int tokens, int num_experts, int topk) {
+B200_EXPORT int64_t b200_moe_sorting_get_workspace_size(int tokens, int num_experts, int topk, int dispatch_policy) {
+    (void)dispatch_policy;  // the size covers both of this library's sort paths
     return sorting_workspace_bytes(tokens, num_experts, topk);
 }
 
@@ -110,10 +112,15 @@ B200_EXPORT int b200_moe_sorting_fwd(const aiter_tensor_t* topk_ids, const aiter
                          aiter_tensor_t* sorted_expert_ids, aiter_tensor_t* num_valid_ids, aiter_tensor_t* moe_buf,
                          int num_experts, int unit_size, const aiter_tensor_t* local_expert_mask,
                          const aiter_tensor_t* num_local_tokens, aiter_tensor_t* workspace, int dispatch_policy,
-                         aiter_tensor_t* local_topk_ids, void* stream) {
+                         aiter_tensor_t* local_topk_ids, aiter_tensor_t* m_indices, aiter_tensor_t* reverse_sorted,
+                         void* stream) {
     (void)dispatch_policy;  // the reference's one-shot / multi-phase choice; made from the sizes here
     return safe_call([&] {
         B200_CHECK(topk_ids != nullptr, "topk_ids must not be NULL");
+        B200_CHECK(m_indices == nullptr, "m_indices (per-row expert index of the grouped-GEMM layout) is not produced by "
+                   "this library: pass NULL");
+        B200_CHECK(reverse_sorted == nullptr, "reverse_sorted (token-slot to sorted-position map) is not produced by this "
+                   "library: pass NULL");
         DeviceGuard g(topk_ids->device_id);
         launch_moe_sorting(topk_ids, topk_weights, sorted_token_ids, sorted_weights, sorted_expert_ids,
                            num_valid_ids, moe_buf, num_experts, unit_size, local_expert_mask, num_local_tokens,
@@ -142,20 +149,21 @@ B200_EXPORT int b200_moe_sorting_fwd_noalloc(const aiter_tensor_t* topk_ids, con
     });
 }
 
-B200_EXPORT int b200_moe_quant_1x128(aiter_tensor_t* out, const aiter_tensor_t* input, aiter_tensor_t* scales, void* stream) {
+B200_EXPORT int b200_moe_quant_1x128(aiter_tensor_t* out, const aiter_tensor_t* input, aiter_tensor_t* scales,
+                                     const aiter_tensor_t* num_rows, int num_rows_factor, int transpose_scale, void* stream) {
     return safe_call([&] {
         B200_CHECK(input != nullptr, "input must not be NULL");
         DeviceGuard g(input->device_id);
-        launch_quant_1x128(out, input, scales, (cudaStream_t)stream);
+        launch_quant_1x128(out, input, scales, num_rows, num_rows_factor, transpose_scale, (cudaStream_t)stream);
     });
 }
 
 B200_EXPORT int b200_moe_quant_per_token(aiter_tensor_t* out, const aiter_tensor_t* input, aiter_tensor_t* scales,
-                                         const aiter_tensor_t* row_limit, void* stream) {
+                                         const aiter_tensor_t* num_rows, int num_rows_factor, void* stream) {
     return safe_call([&] {
         B200_CHECK(input != nullptr, "input must not be NULL");
         DeviceGuard g(input->device_id);
-        launch_quant_per_token(out, input, scales, row_limit, (cudaStream_t)stream);
+        launch_quant_per_token(out, input, scales, num_rows, num_rows_factor, (cudaStream_t)stream);
     });
 }
 
@@ -227,32 +235,32 @@ B200_EXPORT int b200_moe_quant_per_tensor(aiter_tensor_t* out, const aiter_tenso
 
 B200_EXPORT int b200_ep_dispatch(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale, const aiter_tensor_t* topk_ids,
                                  const aiter_tensor_t* peer_a1, const aiter_tensor_t* peer_a1_scale, int rank, int world,
-                                 int experts_per_rank, void* stream) {
+                                 int experts_per_rank, const aiter_tensor_t* expert_rank, void* stream) {
     return safe_call([&] {
         B200_CHECK(a1 != nullptr, "a1 must not be NULL");
         DeviceGuard g(a1->device_id);
-        launch_ep_dispatch(a1, a1_scale, topk_ids, peer_a1, peer_a1_scale, rank, world, experts_per_rank,
+        launch_ep_dispatch(a1, a1_scale, topk_ids, peer_a1, peer_a1_scale, rank, world, experts_per_rank, expert_rank,
                            (cudaStream_t)stream);
     });
 }
 
 B200_EXPORT int b200_ep_push_partials(const aiter_tensor_t* acc, const aiter_tensor_t* topk_ids,
                                       const aiter_tensor_t* peer_recv, int rank, int world, int experts_per_rank,
-                                      void* stream) {
+                                      const aiter_tensor_t* expert_rank, void* stream) {
     return safe_call([&] {
         B200_CHECK(acc != nullptr, "acc must not be NULL");
         DeviceGuard g(acc->device_id);
-        launch_ep_push(acc, topk_ids, peer_recv, rank, world, experts_per_rank, (cudaStream_t)stream);
+        launch_ep_push(acc, topk_ids, peer_recv, rank, world, experts_per_rank, expert_rank, (cudaStream_t)stream);
     });
 }
 
 B200_EXPORT int b200_ep_combine(aiter_tensor_t* out, const aiter_tensor_t* acc, const aiter_tensor_t* recv,
                                 const aiter_tensor_t* topk_ids, int rank, int world, int experts_per_rank,
-                                void* stream) {
+                                const aiter_tensor_t* expert_rank, void* stream) {
     return safe_call([&] {
         B200_CHECK(acc != nullptr, "acc must not be NULL");
         DeviceGuard g(acc->device_id);
-        launch_ep_combine(out, acc, recv, topk_ids, rank, world, experts_per_rank, (cudaStream_t)stream);
+        launch_ep_combine(out, acc, recv, topk_ids, rank, world, experts_per_rank, expert_rank, (cudaStream_t)stream);
     });
 }
 

@@ -38,14 +38,16 @@ constexpr int kEpThreads = 256;
 constexpr int kMaxWorld = 64;
 
 // bit r set: token has a route to an expert of rank r
+// expert_rank (optional): [global experts] owning rank of every expert, for placements that are not contiguous
+// slices (a placement balanced by routing statistics); NULL = expert e lives on rank e / experts_per_rank.
 __device__ __forceinline__ unsigned long long touch_mask(const int* __restrict__ ids, int topk, int experts_per_rank,
-                                                         int world) {
+                                                         int world, const int* __restrict__ expert_rank) {
     unsigned long long m = 0;
     for (int k = 0; k < topk; ++k) {
         const int e = ids[k];
         if (e >= 0) {
-            const int r = e / experts_per_rank;
-            if (r < world) m |= 1ull << r;
+            const int r = expert_rank ? __ldg(expert_rank + e) : e / experts_per_rank;
+            if (r >= 0 && r < world) m |= 1ull << r;
         }
     }
     return m;
@@ -54,11 +56,11 @@ __device__ __forceinline__ unsigned long long touch_mask(const int* __restrict__
 __global__ void __launch_bounds__(kEpThreads) ep_push_kernel(const float4* __restrict__ acc, const int* __restrict__ topk_ids,
                                                              const long long* __restrict__ peer_recv, int M, int H4,
                                                              int topk, int rank, int world, int experts_per_rank,
-                                                             int m_local) {
+                                                             int m_local, const int* __restrict__ expert_rank) {
     for (int t = blockIdx.x; t < M; t += gridDim.x) {
         const int owner = t / m_local;
         if (owner == rank) continue;
-        const unsigned long long m = touch_mask(topk_ids + (size_t)t * topk, topk, experts_per_rank, world);
+        const unsigned long long m = touch_mask(topk_ids + (size_t)t * topk, topk, experts_per_rank, world, expert_rank);
         if (!((m >> rank) & 1ull)) continue;
         const float4* src = acc + (size_t)t * H4;
         float4* dst = reinterpret_cast<float4*>(peer_recv[owner]) + ((size_t)rank * m_local + (t - owner * m_local)) * H4;
@@ -73,9 +75,10 @@ __global__ void __launch_bounds__(kEpThreads) ep_dispatch_kernel(const uint4* __
                                                                  const int* __restrict__ topk_ids,
                                                                  const long long* __restrict__ peer_a1,
                                                                  const long long* __restrict__ peer_a1s, int m_local, int H16,
-                                                                 int KB, int topk, int rank, int world, int experts_per_rank) {
+                                                                 int KB, int topk, int rank, int world, int experts_per_rank,
+                                                                 const int* __restrict__ expert_rank) {
     for (int tl = blockIdx.x; tl < m_local; tl += gridDim.x) {
-        const unsigned long long m = touch_mask(topk_ids + (size_t)tl * topk, topk, experts_per_rank, world);
+        const unsigned long long m = touch_mask(topk_ids + (size_t)tl * topk, topk, experts_per_rank, world, expert_rank);
         const size_t t = (size_t)rank * m_local + tl;
         for (int r = 0; r < world; ++r) {
             if (!((m >> r) & 1ull)) continue;
@@ -99,10 +102,11 @@ template <typename T2>
 __global__ void __launch_bounds__(kEpThreads) ep_combine_kernel(uint2* __restrict__ out, const float4* __restrict__ acc,
                                                                 const float4* __restrict__ recv,
                                                                 const int* __restrict__ topk_ids, int H4, int topk, int rank,
-                                                                int world, int experts_per_rank, int m_local) {
+                                                                int world, int experts_per_rank, int m_local,
+                                                                const int* __restrict__ expert_rank) {
     for (int tl = blockIdx.x; tl < m_local; tl += gridDim.x) {
         const int t = rank * m_local + tl;
-        const unsigned long long m = touch_mask(topk_ids + (size_t)t * topk, topk, experts_per_rank, world);
+        const unsigned long long m = touch_mask(topk_ids + (size_t)t * topk, topk, experts_per_rank, world, expert_rank);
         for (int i = threadIdx.x; i < H4; i += kEpThreads) {
             float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
             for (int r = 0; r < world; ++r) {
@@ -114,6 +118,12 @@ __global__ void __launch_bounds__(kEpThreads) ep_combine_kernel(uint2* __restric
             out[(size_t)tl * H4 + i] = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
         }
     }
+}
+
+const int* rank_table(const aiter_tensor_t* expert_rank) {
+    if (!expert_rank) return nullptr;
+    check_tensor(expert_rank, "expert_rank", AITER_DTYPE_i32, 1);
+    return (const int*)expert_rank->ptr;
 }
 
 void check_common(const aiter_tensor_t* acc, const aiter_tensor_t* topk_ids, int rank, int world, int experts_per_rank,
@@ -135,7 +145,7 @@ void check_common(const aiter_tensor_t* acc, const aiter_tensor_t* topk_ids, int
 
 void launch_ep_dispatch(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale, const aiter_tensor_t* topk_ids,
                         const aiter_tensor_t* peer_a1, const aiter_tensor_t* peer_a1_scale, int rank, int world,
-                        int experts_per_rank, cudaStream_t stream) {
+                        int experts_per_rank, const aiter_tensor_t* expert_rank, cudaStream_t stream) {
     check_tensor(a1, "a1", AITER_DTYPE_fp8, 2);
     check_tensor(a1_scale, "a1_scale", AITER_DTYPE_fp32, 2);
     check_tensor(topk_ids, "topk_ids", AITER_DTYPE_i32, 2);
@@ -153,12 +163,13 @@ void launch_ep_dispatch(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale
     ep_dispatch_kernel<<<grid, kEpThreads, 0, stream>>>((const uint4*)a1->ptr, (const uint32_t*)a1_scale->ptr,
                                                        (const int*)topk_ids->ptr, (const long long*)peer_a1->ptr,
                                                        (const long long*)peer_a1_scale->ptr, (int)m_local, (int)(H / 16),
-                                                       (int)KB, (int)topk_ids->shape[1], rank, world, experts_per_rank);
+                                                       (int)KB, (int)topk_ids->shape[1], rank, world, experts_per_rank,
+                                                       rank_table(expert_rank));
     B200_CUDA(cudaGetLastError());
 }
 
 void launch_ep_push(const aiter_tensor_t* acc, const aiter_tensor_t* topk_ids, const aiter_tensor_t* peer_recv, int rank,
-                    int world, int experts_per_rank, cudaStream_t stream) {
+                    int world, int experts_per_rank, const aiter_tensor_t* expert_rank, cudaStream_t stream) {
     int64_t M, H, topk, m_local;
     check_common(acc, topk_ids, rank, world, experts_per_rank, M, H, topk, m_local);
     check_tensor(peer_recv, "peer_recv", AITER_DTYPE_i64, 1);
@@ -167,12 +178,13 @@ void launch_ep_push(const aiter_tensor_t* acc, const aiter_tensor_t* topk_ids, c
     const int grid = (int)std::min<int64_t>(M, (int64_t)sm_count(acc->device_id) * 8);
     ep_push_kernel<<<grid, kEpThreads, 0, stream>>>((const float4*)acc->ptr, (const int*)topk_ids->ptr,
                                                    (const long long*)peer_recv->ptr, (int)M, (int)(H / 4), (int)topk, rank,
-                                                   world, experts_per_rank, (int)m_local);
+                                                   world, experts_per_rank, (int)m_local, rank_table(expert_rank));
     B200_CUDA(cudaGetLastError());
 }
 
 void launch_ep_combine(aiter_tensor_t* out, const aiter_tensor_t* acc, const aiter_tensor_t* recv,
-                       const aiter_tensor_t* topk_ids, int rank, int world, int experts_per_rank, cudaStream_t stream) {
+                       const aiter_tensor_t* topk_ids, int rank, int world, int experts_per_rank,
+                       const aiter_tensor_t* expert_rank, cudaStream_t stream) {
     int64_t M, H, topk, m_local;
     check_common(acc, topk_ids, rank, world, experts_per_rank, M, H, topk, m_local);
     check_tensor(out, "out", -1, 2);
@@ -187,11 +199,11 @@ void launch_ep_combine(aiter_tensor_t* out, const aiter_tensor_t* acc, const ait
     if (out->dtype_ == AITER_DTYPE_bf16)
         ep_combine_kernel<__nv_bfloat162><<<grid, kEpThreads, 0, stream>>>(
             (uint2*)out->ptr, (const float4*)acc->ptr, (const float4*)recv->ptr, (const int*)topk_ids->ptr, (int)(H / 4),
-            (int)topk, rank, world, experts_per_rank, (int)m_local);
+            (int)topk, rank, world, experts_per_rank, (int)m_local, rank_table(expert_rank));
     else
         ep_combine_kernel<__half2><<<grid, kEpThreads, 0, stream>>>(
             (uint2*)out->ptr, (const float4*)acc->ptr, (const float4*)recv->ptr, (const int*)topk_ids->ptr, (int)(H / 4),
-            (int)topk, rank, world, experts_per_rank, (int)m_local);
+            (int)topk, rank, world, experts_per_rank, (int)m_local, rank_table(expert_rank));
     B200_CUDA(cudaGetLastError());
 }
 

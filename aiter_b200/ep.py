@@ -31,14 +31,20 @@ import torch
 import torch.distributed as dist
 
 from . import _lib, dtypes
-from .fused_moe import _mark, fused_moe_stages, per_group_quant_hip
+from .enums import QuantType
+from .fused_moe import _mark, fused_moe_stages, per_group_quant_hip, per_token_quant_hip
 
 
 _MASKS: dict = {}
 
 
-def expert_mask_for_rank(num_experts: int, rank: int, world: int, device=None) -> torch.Tensor:
-    """[global_E] int32, 1 for the contiguous slice of experts owned by ``rank``."""
+def expert_mask_for_rank(num_experts: int, rank: int, world: int, device=None, expert_rank=None) -> torch.Tensor:
+    """[global_E] int32, 1 for the experts owned by ``rank``: the contiguous slice [rank*E/G, (rank+1)*E/G), or the
+    entries of ``expert_rank`` ([global_E] int32, owning rank per expert) equal to ``rank``. The sort numbers the
+    local experts in ascending global id, which is the order the rank's weight slices must have
+    (``local_experts_of``)."""
+    if expert_rank is not None:
+        return (expert_rank.to(device) == rank).to(torch.int32)
     if num_experts % world != 0:
         raise ValueError(f"num_experts ({num_experts}) must be divisible by the EP world size ({world})")
     key = (num_experts, rank, world, str(device))
@@ -51,16 +57,45 @@ def expert_mask_for_rank(num_experts: int, rank: int, world: int, device=None) -
     return mask
 
 
+def balanced_expert_placement(route_counts, world: int) -> torch.Tensor:
+    """Expert -> rank table [E] int32 with E/world experts per rank and the per-rank route totals levelled:
+    experts in descending order of ``route_counts`` (routes per expert on a calibration batch) each go to the
+    rank with the smallest total that still has a free slot. What a weight loader would run once, from routing
+    statistics, to place the experts; contiguous slices leave the hottest rank 1.4x above the mean on the
+    DeepSeek-V3 benchmark routing."""
+    counts = torch.as_tensor(route_counts).to(torch.int64).cpu()
+    E = counts.numel()
+    if E % world != 0:
+        raise ValueError(f"num_experts ({E}) must be divisible by the EP world size ({world})")
+    per = E // world
+    load = [0] * world
+    free = [per] * world
+    table = torch.empty(E, dtype=torch.int32)
+    for e in torch.argsort(counts, descending=True, stable=True).tolist():
+        r = min((r for r in range(world) if free[r] > 0), key=lambda r: (load[r], r))
+        table[e] = r
+        load[r] += int(counts[e])
+        free[r] -= 1
+    return table
+
+
+def local_experts_of(expert_rank, rank: int) -> torch.Tensor:
+    """Global ids of the experts ``rank`` owns under ``expert_rank``, ascending: local expert i of that rank."""
+    return torch.nonzero(torch.as_tensor(expert_rank).cpu() == rank).flatten()
+
+
 def _gpu_local_layer(a1, a1_scale, w1, w2, topk_weight, topk_ids, expert_mask, w1_scale, w2_scale, timers=None,
-                     chunks=1, on_chunk=None, sm_margin=0):
+                     chunks=1, on_chunk=None, sm_margin=0, quant_type=QuantType.per_1x128):
     """All rows, local experts -> fp32 partial [M, H] (or [chunks, M, H/chunks]); no final rounding."""
     return fused_moe_stages(a1, w1, w2, topk_weight, topk_ids, expert_mask, w1_scale, w2_scale,
                             a1_scale, None, None, timers=timers, stage2_chunks=chunks, on_chunk=on_chunk,
-                            sm_margin=sm_margin)
+                            sm_margin=sm_margin, quant_type=quant_type)
 
 
-def _gpu_quant(x):
-    return per_group_quant_hip(x)
+def _gpu_quant(x, quant_type=QuantType.per_1x128):
+    if QuantType(quant_type) == QuantType.per_Token:
+        return per_token_quant_hip(x, quant_dtype=dtypes.fp8)
+    return per_group_quant_hip(x, quant_dtype=dtypes.fp8)
 
 
 def _gpu_finalize(acc, dtype):
@@ -145,25 +180,25 @@ class PeerExchange:
         return cls._cache[key]
 
 
-def _p2p_combine(ex, partial, ids, num_experts, group, dtype, timers):
+def _p2p_combine(ex, partial, ids, num_experts, group, dtype, timers, expert_rank=None):
     """partial [M, H] fp32 of this rank -> out [M/G, H]: push, barrier, combine."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     M, H = partial.shape
     m_local = M // world
     epr = num_experts // world
-    _lib.call("b200_ep_push_partials", partial, ids, ex.ptrs_recv, rank, world, epr, device=partial.device)
+    _lib.call("b200_ep_push_partials", partial, ids, ex.ptrs_recv, rank, world, epr, expert_rank, device=partial.device)
     _mark(timers, "ep_barrier")
     dist.all_reduce(ex.flag, group=group)   # passes only after every rank's push kernel has completed
     _mark(timers, "ep_combine")
     out = torch.empty((m_local, H), dtype=dtype, device=partial.device)
-    _lib.call("b200_ep_combine", out, partial, ex.recv, ids, rank, world, epr, device=partial.device)
+    _lib.call("b200_ep_combine", out, partial, ex.recv, ids, rank, world, epr, expert_rank, device=partial.device)
     return out
 
 
 def ep_fused_moe(x_local, w1_local, w2_local, topk_weight_local, topk_ids_local, w1_scale_local,
                  w2_scale_local, num_experts, group=None, dtype=torch.bfloat16,
                  quant=_gpu_quant, local_layer=_gpu_local_layer, finalize=_gpu_finalize, timers=None,
-                 overlap_chunks=None, sm_margin=16, exchange="nccl"):
+                 overlap_chunks=None, sm_margin=16, exchange="nccl", quant_type=QuantType.per_1x128, expert_rank=None):
     """x_local [M/G, H] bf16, routing [M/G, topk] with GLOBAL expert ids -> out [M/G, H].
 
     Every rank must pass the same number of rows. With ``overlap_chunks`` > 1 stage 2 runs in that many
@@ -171,14 +206,29 @@ def ep_fused_moe(x_local, w1_local, w2_local, topk_weight_local, topk_ids_local,
     ``sm_margin`` SMs are kept free for NCCL during those launches. Off by default: on 8 B200s four ranges
     of 59 MB took as long in total as one 235 MB reduce-scatter after the unsplit stage 2 (1.47 vs 1.40 ms).
     ``exchange``: "nccl" = fp32 reduce-scatter of the partials; "p2p" = push of the produced rows into the
-    owner's memory + combine (see the module docstring; the first call builds the IPC mappings)."""
+    owner's memory + combine (see the module docstring; the first call builds the IPC mappings).
+    ``expert_rank``: optional [num_experts] int32 device tensor, the rank that owns each expert (a placement from
+    ``balanced_expert_placement``); the rank's weights are then its experts in ascending global id. Default:
+    contiguous slices.
+    ``quant_type``: per_1x128 / per_128x128 (both exchanges) or per_Token (NCCL exchange: one scale per row travels
+    with the codes)."""
     world = dist.get_world_size(group)
     rank = dist.get_rank(group)
     m_local, H = x_local.shape
     topk = topk_ids_local.shape[1]
     dev = x_local.device
+    quant_type = QuantType(quant_type)
+    if quant_type == QuantType.per_128x128:
+        quant_type = QuantType.per_1x128
+    if quant_type not in (QuantType.per_1x128, QuantType.per_Token):
+        raise NotImplementedError(f"ep_fused_moe: quant_type={quant_type!r} is not supported (per_1x128, per_Token)")
+    if quant_type == QuantType.per_Token and exchange == "p2p":
+        raise NotImplementedError("ep_fused_moe: the peer-memory exchange carries 1x128 scales; use exchange='nccl' "
+                                  "with QuantType.per_Token")
+    layer_kw = {} if quant_type == QuantType.per_1x128 else {"quant_type": quant_type}
     _mark(timers, "ep_quant")
-    a1_l, a1s_l = quant(x_local)
+    a1_l, a1s_l = quant(x_local) if quant_type == QuantType.per_1x128 else quant(x_local, quant_type)
+    a1s_l = a1s_l.view(m_local, -1)
     _mark(timers, "ep_all_gather")
     ex = None
     if exchange not in ("nccl", "p2p"):
@@ -192,7 +242,7 @@ def ep_fused_moe(x_local, w1_local, w2_local, topk_weight_local, topk_ids_local,
         ex = PeerExchange.get(group, m_local, H, dev)
         ids_l = topk_ids_local.contiguous()
         _lib.call("b200_ep_dispatch", a1_l, a1s_l.view(m_local, -1), ids_l, ex.ptrs_a1, ex.ptrs_a1_scale, rank, world,
-                  num_experts // world, device=dev)
+                  num_experts // world, expert_rank, device=dev)
         side_l = torch.cat([ids_l.view(torch.int32), topk_weight_local.contiguous().view(torch.int32)], dim=1)
         side = torch.empty((world * m_local, side_l.shape[1]), dtype=torch.int32, device=dev)
         dist.all_gather_into_tensor(side, side_l, group=group)
@@ -212,7 +262,7 @@ def ep_fused_moe(x_local, w1_local, w2_local, topk_weight_local, topk_ids_local,
         a1s = side[:, :kb].contiguous().view(torch.float32)
         ids = side[:, kb:kb + topk].contiguous()
         wts = side[:, kb + topk:].contiguous().view(torch.float32)
-    mask = expert_mask_for_rank(num_experts, rank, world, device=dev)
+    mask = expert_mask_for_rank(num_experts, rank, world, device=dev, expert_rank=expert_rank)
     if overlap_chunks is None:
         overlap_chunks = 1   # measured on 8 x B200: the ranged reduce-scatters gain nothing over one call
     if overlap_chunks > 1 and ex is not None:
@@ -228,7 +278,7 @@ def ep_fused_moe(x_local, w1_local, w2_local, topk_weight_local, topk_ids_local,
                                                     async_op=True))
 
         partial = local_layer(a1, a1s, w1_local, w2_local, wts, ids, mask, w1_scale_local, w2_scale_local,
-                              timers=timers, chunks=overlap_chunks, on_chunk=on_chunk, sm_margin=sm_margin)
+                              timers=timers, chunks=overlap_chunks, on_chunk=on_chunk, sm_margin=sm_margin, **layer_kw)
         if timers is not None:
             timers.pop()
         _mark(timers, "ep_reduce_scatter")
@@ -242,13 +292,13 @@ def ep_fused_moe(x_local, w1_local, w2_local, topk_weight_local, topk_ids_local,
         return out
     if timers is not None:
         partial = local_layer(a1, a1s, w1_local, w2_local, wts, ids, mask, w1_scale_local, w2_scale_local,
-                              timers=timers)
+                              timers=timers, **layer_kw)
         timers.pop()   # the local layer's own "end" mark: the next mark takes its place
     else:
-        partial = local_layer(a1, a1s, w1_local, w2_local, wts, ids, mask, w1_scale_local, w2_scale_local)
+        partial = local_layer(a1, a1s, w1_local, w2_local, wts, ids, mask, w1_scale_local, w2_scale_local, **layer_kw)
     if ex is not None:
         _mark(timers, "ep_push")
-        out = _p2p_combine(ex, partial, ids, num_experts, group, dtype, timers)
+        out = _p2p_combine(ex, partial, ids, num_experts, group, dtype, timers, expert_rank)
         _mark(timers, "end")
         return out
     _mark(timers, "ep_reduce_scatter")

@@ -45,9 +45,10 @@ def check_device_status(device=None) -> None:
 
 
 # ------------------------------------------------------------------------------------- sorting
-def moe_sorting_get_workspace_size(tokens: int, num_experts: int, topk: int) -> int:
+def moe_sorting_get_workspace_size(tokens: int, num_experts: int, topk: int, dispatch_policy: int = 0) -> int:
     """aiter/ops/moe_sorting_opus.py:12-18."""
-    return int(_lib.lib().b200_moe_sorting_get_workspace_size(int(tokens), int(num_experts), int(topk)))
+    return int(_lib.lib().b200_moe_sorting_get_workspace_size(int(tokens), int(num_experts), int(topk),
+                                                              int(dispatch_policy)))
 
 
 def moe_sorting(
@@ -104,7 +105,7 @@ def _moe_sorting_impl(topk_ids, topk_weights, num_experts, model_dim, moebuf_dty
         "b200_moe_sorting_fwd",
         topk_ids.contiguous(), topk_weights.contiguous(), sorted_ids, sorted_weights, sorted_expert_ids,
         num_valid_ids, moe_buf if moe_buf.numel() > 0 else None, int(num_experts), block_size,
-        expert_mask, num_local_tokens, workspace, int(dispatch_policy), local_topk_ids,
+        expert_mask, num_local_tokens, workspace, int(dispatch_policy), local_topk_ids, None, None,
         device=device,
     )
     ret = (sorted_ids, sorted_weights, sorted_expert_ids, num_valid_ids, moe_buf)
@@ -114,59 +115,61 @@ def _moe_sorting_impl(topk_ids, topk_weights, num_experts, model_dim, moebuf_dty
 
 
 # ------------------------------------------------------------------------------------- quant
-def per_group_quant_hip(x, scale=None, quant_dtype=dtypes.fp8, group_size=128, transpose_scale=False,
-                        num_rows=None, num_rows_factor=1):
-    """1x128 dynamic FP8 quantisation, signature of aiter/ops/quant.py:439-483.
-    x [..., C] bf16 -> (codes [..., C] e4m3, scales [rows, C/128] fp32)."""
-    if group_size != 128:
-        raise NotImplementedError("per_group_quant_hip: only group_size=128 is supported")
+_ACT_DTYPES = (dtypes.bf16, dtypes.fp16)
+
+
+def _check_quant_args(fn, x, scale, quant_dtype):
+    if scale is not None:
+        # aiter/ops/quant.py:419-420, 454-455: the reference raises the same way
+        raise ValueError("unsupported: static per token quant")
     if quant_dtype != dtypes.fp8:
-        raise NotImplementedError("per_group_quant_hip: only quant_dtype=fp8 (e4m3fn) is supported")
-    if transpose_scale:
-        raise NotImplementedError("per_group_quant_hip: transpose_scale=True is not supported")
-    if scale is not None or num_rows is not None:
-        raise NotImplementedError("per_group_quant_hip: static scale / num_rows are not supported")
-    if x.dtype != dtypes.bf16:
-        raise NotImplementedError(f"per_group_quant_hip: input must be bf16, got {x.dtype}")
+        raise NotImplementedError(f"{fn}: quant_dtype={quant_dtype} is not supported, only dtypes.fp8 (e4m3fn); "
+                                  "pass quant_dtype=dtypes.fp8 (the reference's default is dtypes.i8)")
+    if x.dtype not in _ACT_DTYPES:
+        raise NotImplementedError(f"{fn}: input must be bf16 or fp16, got {x.dtype}")
+    if not x.is_cuda:
+        raise RuntimeError(f"{fn}: input must be a CUDA tensor (there is no CPU path)")
+
+
+def per_group_quant_hip(x, scale=None, quant_dtype=dtypes.i8, group_size=128, transpose_scale=False,
+                        num_rows=None, num_rows_factor=1, scale_type=dtypes.fp32):
+    """Per-row, per-128-column dynamic FP8 quantisation; parameter list of aiter/ops/quant.py:439-448.
+
+    x [..., C] bf16|fp16 -> (codes [..., C] e4m3, scales [..., C/128] fp32). ``num_rows``: device int32 [1],
+    only the first num_rows*num_rows_factor rows are written. ``transpose_scale``: the scale buffer keeps its
+    shape but holds the [C/128, rows] transpose (the layout the reference's 1-stage kernels read,
+    aiter/fused_moe.py:1138-1147). Only quant_dtype=dtypes.fp8, group_size=128 and fp32 scales exist here."""
+    _check_quant_args("per_group_quant_hip", x, scale, quant_dtype)
+    if group_size != 128:
+        raise NotImplementedError(f"per_group_quant_hip: group_size={group_size} is not supported, only 128")
+    if scale_type != dtypes.fp32:
+        raise NotImplementedError(f"per_group_quant_hip: scale_type={scale_type} is not supported, only fp32")
     x = x.contiguous()
     cols = x.shape[-1]
-    rows = x.numel() // cols
     y = torch.empty(x.shape, dtype=dtypes.fp8, device=x.device)
-    y_scale = torch.empty((rows, cols // 128), dtype=dtypes.fp32, device=x.device)
-    _lib.call("b200_moe_quant_1x128", y, x, y_scale, device=x.device)
+    y_scale = torch.empty((*x.shape[:-1], cols // 128), dtype=dtypes.fp32, device=x.device)
+    _lib.call("b200_moe_quant_1x128", y, x, y_scale, num_rows, int(num_rows_factor), int(bool(transpose_scale)),
+              device=x.device)
     return y, y_scale
 
 
-def per_token_quant_hip(x, scale=None, quant_dtype=dtypes.fp8, row_limit=None):
-    """Per-row dynamic FP8 quantisation, signature of aiter/ops/quant.py:406-436.
-    x [..., C] bf16 -> (codes [..., C] e4m3, scales [..., 1] fp32). ``row_limit``: optional device int32
-    [1]; rows at or past it are left untouched."""
-    if scale is not None:
-        raise NotImplementedError("per_token_quant_hip: static scale is not supported")
-    if quant_dtype != dtypes.fp8:
-        raise NotImplementedError("per_token_quant_hip: only quant_dtype=fp8 (e4m3fn) is supported")
-    if x.dtype != dtypes.bf16:
-        raise NotImplementedError(f"per_token_quant_hip: input must be bf16, got {x.dtype}")
+def per_token_quant_hip(x, scale=None, quant_dtype=dtypes.i8, num_rows=None, num_rows_factor=1):
+    """Per-row dynamic FP8 quantisation; parameter list of aiter/ops/quant.py:406-413.
+    x [..., C] bf16|fp16 -> (codes [..., C] e4m3, scales [..., 1] fp32). ``num_rows``: device int32 [1]; rows at or
+    past num_rows*num_rows_factor are left untouched. Only quant_dtype=dtypes.fp8 exists here."""
+    _check_quant_args("per_token_quant_hip", x, scale, quant_dtype)
     x = x.contiguous()
     cols = x.shape[-1]
     x2 = x.view(-1, cols)
     y = torch.empty(x2.shape, dtype=dtypes.fp8, device=x.device)
     y_scale = torch.empty((x2.shape[0],), dtype=dtypes.fp32, device=x.device)
-    _lib.call("b200_moe_quant_per_token", y, x2, y_scale, row_limit, device=x.device)
+    _lib.call("b200_moe_quant_per_token", y, x2, y_scale, num_rows, int(num_rows_factor), device=x.device)
     return y.view(x.shape), y_scale.view(*x.shape[:-1], 1)
 
 
-def per_tensor_quant_hip(x, scale=None, quant_dtype=dtypes.fp8, num_rows=None, num_rows_factor=1, row_limit=None,
-                         want_row_scales=False):
-    """Per-tensor dynamic FP8 quantisation, signature of aiter/ops/quant.py:628-645.
-    x [..., C] bf16 -> (codes e4m3, scale [1] fp32). ``row_limit``: optional device int32 [1], rows at or past it
-    take no part; ``want_row_scales`` also returns the scale repeated once per row (what the GEMM kernels read)."""
-    if scale is not None or num_rows is not None:
-        raise NotImplementedError("per_tensor_quant_hip: static scale / num_rows are not supported")
-    if quant_dtype != dtypes.fp8:
-        raise NotImplementedError("per_tensor_quant_hip: only quant_dtype=fp8 (e4m3fn) is supported")
-    if x.dtype != dtypes.bf16:
-        raise NotImplementedError(f"per_tensor_quant_hip: input must be bf16, got {x.dtype}")
+def _per_tensor_quant(x, row_limit=None, want_row_scales=False):
+    """Dynamic per-tensor FP8 quantisation with the two extras the layer needs: ``row_limit`` (device int32 [1],
+    rows at or past it take no part) and the scale repeated once per row (what the GEMM kernels read)."""
     x = x.contiguous()
     x2 = x.view(-1, x.shape[-1])
     y = torch.empty(x2.shape, dtype=dtypes.fp8, device=x.device)
@@ -174,13 +177,25 @@ def per_tensor_quant_hip(x, scale=None, quant_dtype=dtypes.fp8, num_rows=None, n
     amax = torch.empty((1,), dtype=dtypes.fp32, device=x.device)
     rows = torch.empty((x2.shape[0],), dtype=dtypes.fp32, device=x.device) if want_row_scales else None
     _lib.call("b200_moe_quant_per_tensor", y, x2, y_scale, amax, rows, row_limit, device=x.device)
-    if want_row_scales:
-        return y.view(x.shape), y_scale, rows
-    return y.view(x.shape), y_scale
+    return y.view(x.shape), y_scale, rows
+
+
+def per_tensor_quant_hip(x, scale=None, quant_dtype=dtypes.i8, num_rows=None, num_rows_factor=1):
+    """Per-tensor dynamic FP8 quantisation; parameter list of aiter/ops/quant.py:628-634.
+    x [..., C] bf16|fp16 -> (codes e4m3, scale [1] fp32). Like the reference, ``num_rows`` is not supported."""
+    assert num_rows is None, "num_rows is not supported for per_tensor_quant_hip"   # aiter/ops/quant.py:635
+    if scale is not None:
+        raise NotImplementedError("per_tensor_quant_hip: static quantisation (scale=...) is not supported")
+    _check_quant_args("per_tensor_quant_hip", x, None, quant_dtype)
+    y, y_scale, _ = _per_tensor_quant(x)
+    return y, y_scale.view(1)
 
 
 def get_hip_quant(qType):
-    """aiter/ops/quant.py:367-387, restricted to the FP8 paths built here."""
+    """aiter/ops/quant.py:367-387, restricted to the FP8 paths built here. Like the reference's table, the
+    per_1x128 entry is ``per_group_quant_hip`` with group_size bound to 128, so callers can pass ``transpose_scale``,
+    ``num_rows`` and ``num_rows_factor`` (aiter/fused_moe.py:1138-1147)."""
+    import functools
     qType = quant_remap.get(QuantType(qType), QuantType(qType))
     if qType == QuantType.per_Token:
         return per_token_quant_hip
@@ -188,7 +203,7 @@ def get_hip_quant(qType):
         return per_tensor_quant_hip
     if qType != QuantType.per_1x128:
         raise NotImplementedError(f"get_hip_quant: only per_1x128 / per_128x128 / per_Token / per_Tensor are supported, got {qType!r}")
-    return per_group_quant_hip
+    return functools.partial(per_group_quant_hip, group_size=128)
 
 
 # ------------------------------------------------------------------------------------- fused_moe
@@ -260,11 +275,11 @@ def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, 
     if hidden_states.dtype == dtypes.fp8:
         a1, a1_s = hidden_states.contiguous(), a1_scale.contiguous().view(M, -1)
     elif per_tensor:
-        a1, _scale, a1_s = per_tensor_quant_hip(hidden_states, want_row_scales=True)
+        a1, _scale, a1_s = _per_tensor_quant(hidden_states, want_row_scales=True)
     elif per_token:
-        a1, a1_s = per_token_quant_hip(hidden_states)
+        a1, a1_s = per_token_quant_hip(hidden_states, quant_dtype=dtypes.fp8)
     else:
-        a1, a1_s = per_group_quant_hip(hidden_states)
+        a1, a1_s = per_group_quant_hip(hidden_states, quant_dtype=dtypes.fp8)
 
     P = sorted_ids.numel()
     status = _status(device)
@@ -282,7 +297,7 @@ def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, 
             _lib.call("b200_moe_quant_per_tensor", a2, a2_bf16, torch.empty((1,), dtype=dtypes.fp32, device=device),
                       torch.empty((1,), dtype=dtypes.fp32, device=device), a2_s, num_valid_ids, device=device)
         else:
-            _lib.call("b200_moe_quant_per_token", a2, a2_bf16, a2_s, num_valid_ids, device=device)
+            _lib.call("b200_moe_quant_per_token", a2, a2_bf16, a2_s, num_valid_ids, 1, device=device)
     else:
         a2 = torch.empty((P, inter_dim), dtype=dtypes.fp8, device=device)
         a2_s = torch.empty((P, inter_dim // 128), dtype=dtypes.fp32, device=device)
@@ -403,8 +418,8 @@ def fused_moe(
             raise ValueError("fused_moe: fp8 hidden_states need a1_scale ([M, model_dim/128], or [M, 1] for per_Token)")
         dtype = dtypes.bf16 if dtype is None else dtype
     else:
-        if hidden_states.dtype != dtypes.bf16:
-            raise NotImplementedError(f"fused_moe: hidden_states must be bf16 or pre-quantised fp8, got {hidden_states.dtype}")
+        if hidden_states.dtype not in (dtypes.bf16, dtypes.fp16):   # aiter/fused_moe.py:752-756
+            raise NotImplementedError(f"fused_moe: hidden_states must be bf16, fp16 or pre-quantised fp8, got {hidden_states.dtype}")
         if a1_scale is not None:
             raise NotImplementedError("fused_moe: a1_scale with un-quantised hidden_states is not supported")
         dtype = hidden_states.dtype if dtype is None else dtype

@@ -54,14 +54,14 @@ typedef struct aiter_tensor_t {
 } aiter_tensor_t;
 
 /* csrc/include/aiter_ctypes_error.h:61-71 */
-int         aiter_ctypes_abi_version(void); /* == 2 */
+int         aiter_ctypes_abi_version(void); /* == 3 */
 const char* aiter_get_last_error(void);     /* NULL when no error is pending */
 void        aiter_clear_last_error(void);
 
 /* Bytes of scratch b200_moe_sorting_fwd needs for this problem (0 when the single-CTA
  * path is taken).  Replaces moe_sorting_opus_get_workspace_size
  * (aiter/ops/moe_sorting_opus.py:12-18, csrc/include/moe_sorting_opus.h:1385-1427). */
-int64_t b200_moe_sorting_get_workspace_size(int tokens, int num_experts, int topk);
+int64_t b200_moe_sorting_get_workspace_size(int tokens, int num_experts, int topk, int dispatch_policy);
 
 /* Stable counting sort of (token, slot) routes by expert, padded per expert to unit_size.
  * Replaces moe_sorting_opus_fwd (csrc/py_itfs_cu/moe_sorting_opus_kernels.cu:14-84,
@@ -74,14 +74,16 @@ int64_t b200_moe_sorting_get_workspace_size(int tokens, int num_experts, int top
  *   local_expert_mask: optional [E] i32, 0 drops the expert and renumbers the others
  *   num_local_tokens: optional [1] i32 read on the device (rows >= it are ignored)
  *   workspace: >= b200_moe_sorting_get_workspace_size bytes when that is > 0
- *   local_topk_ids: optional [M,topk] i32 output, local expert id per route or -1 */
+ *   local_topk_ids: optional [M,topk] i32 output, local expert id per route or -1
+ *   m_indices, reverse_sorted: outputs of the reference's grouped-GEMM layout; not produced here, must be NULL */
 int b200_moe_sorting_fwd(const aiter_tensor_t* topk_ids, const aiter_tensor_t* topk_weights,
                          aiter_tensor_t* sorted_token_ids, aiter_tensor_t* sorted_weights,
                          aiter_tensor_t* sorted_expert_ids, aiter_tensor_t* num_valid_ids,
                          aiter_tensor_t* moe_buf, int num_experts, int unit_size,
                          const aiter_tensor_t* local_expert_mask,
                          const aiter_tensor_t* num_local_tokens, aiter_tensor_t* workspace,
-                         int dispatch_policy, aiter_tensor_t* local_topk_ids, void* stream);
+                         int dispatch_policy, aiter_tensor_t* local_topk_ids, aiter_tensor_t* m_indices,
+                         aiter_tensor_t* reverse_sorted, void* stream);
 
 /* No counterpart in the reference.  The same sort for callers that cannot allocate or pass a
  * workspace: a host runtime bound over an FFI that owns no device allocator, a serving loop whose
@@ -104,23 +106,27 @@ int b200_moe_sorting_fwd_noalloc(const aiter_tensor_t* topk_ids, const aiter_ten
  * codes = RNE(x / scale).  Replaces dynamic_per_token_scaled_quant with group_size=128
  * (aiter/ops/quant.py:439-483, csrc/kernels/quant_kernels.cu:27-167,720-830) with the
  * rounding sequence of the torch oracle (aiter/ops/quant.py:64-94).
- *   input [R,C] bf16 (C % 128 == 0) -> out [R,C] fp8, scales [R,C/128] fp32 */
+ *   input [R,C] bf16|fp16 (C % 128 == 0) -> out [R,C] fp8, scales [R,C/128] fp32
+ *   num_rows: optional [1] i32 on the device; only the first *num_rows * num_rows_factor rows are quantised
+ *   transpose_scale != 0: the scale of (row, column group) is written at [column group * rows + row] of the same
+ *   buffer (rows = the dynamic row count when num_rows is given), the layout the reference's 1-stage kernels read
+ *   (shuffle_scale, csrc/kernels/quant_kernels.cu:143-146; aiter/fused_moe.py:1138-1147) */
 int b200_moe_quant_1x128(aiter_tensor_t* out, const aiter_tensor_t* input, aiter_tensor_t* scales,
-                         void* stream);
+                         const aiter_tensor_t* num_rows, int num_rows_factor, int transpose_scale, void* stream);
 
 /* Dynamic per-row FP8 e4m3 quantisation over the whole row (QuantType.per_Token): scale = amax/448
  * (1 when amax is 0), codes = RNE(x / scale). Replaces dynamic_per_token_scaled_quant
  * (aiter/ops/quant.py:406-436, csrc/kernels/quant_kernels.cu) with the rounding sequence of pertoken_quant
  * (aiter/ops/quant.py:64-94).
- *   input [R,C] bf16 -> out [R,C] fp8, scales [R] fp32; row_limit: optional [1] i32 on the device, rows >= it
- *   are skipped (the padded tail of a sorted buffer) */
+ *   input [R,C] bf16|fp16 -> out [R,C] fp8, scales [R] fp32; num_rows: optional [1] i32 on the device, rows >=
+ *   *num_rows * num_rows_factor are skipped (the padded tail of a sorted buffer) */
 int b200_moe_quant_per_token(aiter_tensor_t* out, const aiter_tensor_t* input, aiter_tensor_t* scales,
-                             const aiter_tensor_t* row_limit, void* stream);
+                             const aiter_tensor_t* num_rows, int num_rows_factor, void* stream);
 
 /* Dynamic per-tensor FP8 e4m3 quantisation (QuantType.per_Tensor): scale = max|x| / 448, codes = RNE(x / scale).
  * Replaces dynamic_per_tensor_quant behind per_tensor_quant_hip (aiter/ops/quant.py:628-645) with the rounding
  * sequence of per_tensor_quant (aiter/ops/quant.py:318-328; like it, no guard for an all-zero tensor).
- *   input [R,C] bf16 -> out [R,C] fp8, scale [1] fp32; amax: [1] fp32 scratch word, cleared by the call;
+ *   input [R,C] bf16|fp16 -> out [R,C] fp8, scale [1] fp32; amax: [1] fp32 scratch word, cleared by the call;
  *   row_scales: optional [R] fp32, receives the scale once per row (the per_Token GEMM kernels take one scale per
  *   row); row_limit: optional [1] i32 on the device, rows >= it take no part (padded tail of a sorted buffer) */
 int b200_moe_quant_per_tensor(aiter_tensor_t* out, const aiter_tensor_t* input, aiter_tensor_t* scale,
@@ -190,14 +196,17 @@ int b200_moe_finalize(aiter_tensor_t* out, const aiter_tensor_t* acc, void* stre
  *     allocation that holds `tensor` and the tensor's byte offset in it; open maps such a handle from another
  *     process for kernels of `device` (the mapping belongs to the device that is current while it is opened, so
  *     every rank opens its peers' handles under its own device) and returns the base address; close unmaps it.
+ * expert_rank: optional [global experts] i32, the rank that owns each expert, for placements that are not contiguous
+ *     slices (NULL: expert e lives on rank e / experts_per_rank).
  * No device-side waiting between ranks; rows that were not pushed are never read. */
 int b200_ep_dispatch(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale, const aiter_tensor_t* topk_ids,
                      const aiter_tensor_t* peer_a1, const aiter_tensor_t* peer_a1_scale, int rank, int world,
-                     int experts_per_rank, void* stream);
+                     int experts_per_rank, const aiter_tensor_t* expert_rank, void* stream);
 int b200_ep_push_partials(const aiter_tensor_t* acc, const aiter_tensor_t* topk_ids, const aiter_tensor_t* peer_recv,
-                          int rank, int world, int experts_per_rank, void* stream);
+                          int rank, int world, int experts_per_rank, const aiter_tensor_t* expert_rank, void* stream);
 int b200_ep_combine(aiter_tensor_t* out, const aiter_tensor_t* acc, const aiter_tensor_t* recv,
-                    const aiter_tensor_t* topk_ids, int rank, int world, int experts_per_rank, void* stream);
+                    const aiter_tensor_t* topk_ids, int rank, int world, int experts_per_rank,
+                    const aiter_tensor_t* expert_rank, void* stream);
 int b200_ep_ipc_export(const aiter_tensor_t* tensor, void* handle_out, int64_t* offset_out);
 int b200_ep_ipc_open(const void* handle, int device, int64_t* ptr_out);
 int b200_ep_ipc_close(int64_t ptr, int device);

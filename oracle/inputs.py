@@ -92,11 +92,13 @@ def make_weights(E, N, K, seed, device="cpu", experts_per_chunk=1, per_token=Fal
     return q, s
 
 
-def make_config(name, seed=0, device="cpu", M=None, E=None):
+def make_config(name, seed=0, device="cpu", M=None, E=None, weights=None):
     """Returns dict(x bf16 [M,H], w1_q, w1_scale, w2_q, w2_scale, topk_weight, topk_ids, cfg).
 
     ``x`` and the routing are always drawn on the CPU generator (so goldens do not depend on
-    the device); ``device`` only selects where the (large) weights are drawn and quantised."""
+    the device); ``device`` only selects where the (large) weights are drawn and quantised. ``weights`` = the
+    (w1_q, w1_scale, w2_q, w2_scale) of an earlier call with the same seed, shapes and quantisation is reused
+    instead of being drawn again (the DeepSeek-V3 cases share 11.3 GB of them)."""
     cfg = dict(CONFIGS[name])
     if M is not None:
         cfg["M"] = M
@@ -105,8 +107,12 @@ def make_config(name, seed=0, device="cpu", M=None, E=None):
     M_, H, I, E_, topk = cfg["M"], cfg["H"], cfg["I"], cfg["E"], cfg["topk"]
     x = torch.randn((M_, H), generator=_gen(seed), dtype=torch.float32).to(torch.bfloat16)
     pt, pten = cfg.get("quant") == "per_token", cfg.get("quant") == "per_tensor"
-    w1_q, w1_s = make_weights(E_, 2 * I, H, seed + 1, device, per_token=pt, per_tensor=pten)
-    w2_q, w2_s = make_weights(E_, H, I, seed + 2, device, per_token=pt, per_tensor=pten)
+    if weights is not None:
+        w1_q, w1_s, w2_q, w2_s = weights
+        assert tuple(w1_q.shape) == (E_, 2 * I, H) and tuple(w2_q.shape) == (E_, H, I)
+    else:
+        w1_q, w1_s = make_weights(E_, 2 * I, H, seed + 1, device, per_token=pt, per_tensor=pten)
+        w2_q, w2_s = make_weights(E_, H, I, seed + 2, device, per_token=pt, per_tensor=pten)
     tw, ti = make_routing(cfg["routing"], M_, E_, topk, seed)
     return dict(x=x.to(device), w1_q=w1_q, w1_scale=w1_s, w2_q=w2_q, w2_scale=w2_s,
                 topk_weight=tw.to(device), topk_ids=ti.to(device), cfg=cfg)

@@ -50,11 +50,11 @@ def test_ctypes_signatures_match_header(lib):
 
 
 def test_abi_version_and_error_channel(lib):
-    assert lib.aiter_ctypes_abi_version() == 2
+    assert lib.aiter_ctypes_abi_version() == 3
     lib.aiter_clear_last_error()
     assert lib.aiter_get_last_error() is None
     # a call with a NULL tensor fails with status -1 and a message, without touching a GPU
-    st = lib.b200_moe_quant_1x128(None, None, None, None)
+    st = lib.b200_moe_quant_1x128(None, None, None, None, 1, 0, None)
     assert st == -1
     assert b"input must not be NULL" in lib.aiter_get_last_error()
     lib.aiter_clear_last_error()

@@ -17,11 +17,12 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-@pytest.mark.parametrize("world,routing,E,topk", [
-    (2, "softmax", 8, 2), (4, "zipf", 8, 2),
-    (8, "dsv3", 64, 8),   # the benchmark's structure in small: 8 groups = 8 ranks, a token's routes on <= 4 of them
+@pytest.mark.parametrize("world,routing,E,topk,placement", [
+    (2, "softmax", 8, 2, "contiguous"), (4, "zipf", 8, 2, "contiguous"),
+    (8, "dsv3", 64, 8, "contiguous"),   # the benchmark's structure in small: 8 groups = 8 ranks, routes on <= 4 of them
+    (4, "zipf", 8, 2, "balanced"), (8, "dsv3", 64, 8, "balanced"),   # expert -> rank table levelled by route counts
 ])
-def test_dispatch_push_combine_emulated_ranks(world, routing, E, topk):
+def test_dispatch_push_combine_emulated_ranks(world, routing, E, topk, placement):
     M, H, I = 256, 512, 256
     g = torch.Generator().manual_seed(world)
     x = torch.randn((M, H), generator=g).to(torch.bfloat16)
@@ -34,6 +35,17 @@ def test_dispatch_push_combine_emulated_ranks(world, routing, E, topk):
     d = lambda t: t.to(dev)
     x, w1_q, w1_s, w2_q, w2_s, tw, ti = map(d, (x, w1_q, w1_s, w2_q, w2_s, tw, ti))
     m_local, epr, kb = M // world, E // world, H // 128
+    if placement == "balanced":
+        counts = torch.bincount(ti.flatten().long().cpu(), minlength=E)
+        table_cpu = ep.balanced_expert_placement(counts, world)
+        assert torch.equal(torch.bincount(table_cpu.long(), minlength=world), torch.full((world,), epr))
+        loads = torch.zeros(world, dtype=torch.long).index_add_(0, table_cpu.long(), counts)
+        contiguous_loads = counts.view(world, epr).sum(1)
+        assert loads.max() <= contiguous_loads.max()
+        xr = table_cpu.to(dev)
+    else:
+        table_cpu = torch.arange(E, dtype=torch.int32) // epr
+        xr = None
     nan_bytes = lambda shape: torch.full(shape, 0x7F, dtype=torch.uint8, device=dev)   # e4m3 NaN codes
     a1_all = [nan_bytes((M, H)).view(torch.float8_e4m3fn) for _ in range(world)]
     a1s_all = [torch.full((M, kb), float("nan"), device=dev) for _ in range(world)]
@@ -44,11 +56,11 @@ def test_dispatch_push_combine_emulated_ranks(world, routing, E, topk):
     # 1. dispatch: every rank stores its rows where they are needed
     for r in range(world):
         rows = slice(r * m_local, (r + 1) * m_local)
-        q, s = per_group_quant_hip(x[rows])
-        _lib.call("b200_ep_dispatch", q, s, ti[rows].contiguous(), p_a1, p_a1s, r, world, epr, device=dev)
+        q, s = per_group_quant_hip(x[rows], quant_dtype=torch.float8_e4m3fn)
+        _lib.call("b200_ep_dispatch", q, s, ti[rows].contiguous(), p_a1, p_a1s, r, world, epr, xr, device=dev)
     # rows arrived exactly where a route exists
-    owner_of_expert = ti // epr
-    q_all, s_all = per_group_quant_hip(x)
+    owner_of_expert = table_cpu.to(dev)[ti.long()]
+    q_all, s_all = per_group_quant_hip(x, quant_dtype=torch.float8_e4m3fn)
     for r in range(world):
         need = (owner_of_expert == r).any(dim=1)
         got = ~torch.isnan(a1s_all[r]).any(dim=1)
@@ -59,16 +71,16 @@ def test_dispatch_push_combine_emulated_ranks(world, routing, E, topk):
     # 2. local layers (non-local routes dropped by the sort), 3. push, 4. combine
     partial = []
     for r in range(world):
-        sl = slice(r * epr, (r + 1) * epr)
-        mask = ep.expert_mask_for_rank(E, r, world, device=dev)
+        sl = ep.local_experts_of(table_cpu, r).to(dev)   # the rank's experts, ascending global id
+        mask = ep.expert_mask_for_rank(E, r, world, device=dev, expert_rank=xr)
         partial.append(fused_moe_stages(a1_all[r], w1_q[sl].contiguous(), w2_q[sl].contiguous(), tw, ti, mask,
                                         w1_s[sl].contiguous(), w2_s[sl].contiguous(), a1s_all[r], None, None))
     for r in range(world):
-        _lib.call("b200_ep_push_partials", partial[r], ti, p_recv, r, world, epr, device=dev)
+        _lib.call("b200_ep_push_partials", partial[r], ti, p_recv, r, world, epr, xr, device=dev)
     outs = []
     for r in range(world):
         out = torch.empty((m_local, H), dtype=torch.bfloat16, device=dev)
-        _lib.call("b200_ep_combine", out, partial[r], recv[r], ti, r, world, epr, device=dev)
+        _lib.call("b200_ep_combine", out, partial[r], recv[r], ti, r, world, epr, xr, device=dev)
         outs.append(out)
     torch.cuda.synchronize()
     aiter_b200.check_device_status()
