@@ -61,6 +61,11 @@ _SIGNATURES = {
 
 _lib = None
 
+# Kernel launches behind one call of an entry point (the sort takes three kernels above 16384 routes, one below;
+# the per-tensor quantiser two). ``launch_count`` adds them up for callers that report how many kernels they ran.
+_KERNELS_PER_CALL = {"b200_moe_quant_per_tensor": 2}
+launch_count = 0
+
 
 def lib():
     """Loads the shared library once; raises if it has not been built."""
@@ -135,6 +140,11 @@ def call(name: str, *args, device: torch.device | None = None):
     if device is None:
         raise RuntimeError(f"{name}: no CUDA tensor among the arguments")
     stream = torch.cuda.current_stream(device).cuda_stream
+    global launch_count
+    if name == "b200_moe_sorting_fwd":
+        launch_count += 3 if args[0].numel() > 16384 else 1
+    else:
+        launch_count += _KERNELS_PER_CALL.get(name, 1)
     status = fn(*cargs, ctypes.c_void_p(stream))
     if status != 0:
         msg = handle.aiter_get_last_error()

@@ -174,10 +174,20 @@ class PeerExchange:
 
     @classmethod
     def get(cls, group, m_local, H, device):
-        key = (id(group) if group is not None else 0, m_local, H, device.index)
+        # keyed by the group's member ranks, not by the object's id (which a later group can reuse)
+        key = (tuple(dist.get_process_group_ranks(group if group is not None else dist.group.WORLD)), m_local, H,
+               device.index)
         if key not in cls._cache:
             cls._cache[key] = cls(group, m_local, H, device)
         return cls._cache[key]
+
+    @classmethod
+    def clear(cls):
+        """Unmaps every peer arena and drops the cache. Call it before ``destroy_process_group`` (a collective point:
+        no kernel of any rank may still be storing into a mapping that is being closed)."""
+        for ex in cls._cache.values():
+            ex.close()
+        cls._cache.clear()
 
 
 def _p2p_combine(ex, partial, ids, num_experts, group, dtype, timers, expert_rank=None):

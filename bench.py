@@ -11,6 +11,10 @@ measured in the same run and reported under "decode".  With N GPUs the experts a
 (expert parallelism: token dispatch, local layer, combine of the fp32 partial sums; over peer memory or
 NCCL) and the total work stays fixed, so scaling is "strong".  Rank 0 prints ONE JSON line.
 
+Beside the headline the same run measures, through the same public calls: the M=64 decode layer ("decode", at
+every N), the Mixtral-shaped per_Token layer and the Qwen3-shaped skewed-routing sweep ("other_configs"), and for
+N > 1 checks a handful of rank-0 output rows against the CPU oracle ("parity_check", outside every timed region).
+
 `--impl reference` times the CPU oracle (the reference's torch arithmetic restated per expert) on
 the host cores over a bounded sample of the same workload.
 """
@@ -35,6 +39,13 @@ H, I, E, TOPK = 7168, 2048, 256, 8
 M_PREFILL, M_DECODE = 8192, 64
 WORKLOAD = "dsv3_fp8_blockscale_moe_prefill_M8192_H7168_I2048_E256_topk8"
 METRIC = "DSV3 FP8-blockscale fused_moe TFLOP/s (M=8192)"
+
+
+# DRAM traffic of one stage-1 launch (dram__bytes_read.sum + dram__bytes_write.sum), per expert, from an `ncu --set
+# full` capture of a small case with the headline's routes per expert; a full launch is this times the expert count
+# (the weights, which make up the traffic, grow with it). Refresh when the GEMM kernel or its tile walk changes.
+STAGE1_DRAM_BYTES_PER_EXPERT = 1.172e9 / 32
+STAGE1_DRAM_CAPTURE = "ncu --set full, moe_gemm_kernel<1>, M=1024 E=32 H=7168 I=2048 topk=8 (256 routes per expert), 2026-11-25"
 
 
 def flops(M):
@@ -301,6 +312,137 @@ def library_fp8_gemm_tflops(dev, n=8192, iters=20):
         return None
 
 
+# ------------------------------------------------------------------------------------------ other configurations
+def quantise_weights_per_channel(E_, N, K, seed, device):
+    """[E_, N, K] ~ N(0, 1/sqrt(K)) quantised to e4m3 with one scale per output channel (QuantType.per_Token weights,
+    op_tests/test_moe_2stage.py:213-214)."""
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    q = torch.empty((E_, N, K), dtype=torch.float8_e4m3fn, device=device)
+    s = torch.empty((E_, N, 1), dtype=torch.float32, device=device)
+    std = 1.0 / (K ** 0.5)
+    for e in range(E_):
+        w = torch.randn((N, K), generator=g, dtype=torch.float32, device=device) * std
+        scale = w.abs().amax(dim=1, keepdim=True) / 448.0
+        scale[scale == 0] = 1.0
+        q[e] = (w / scale).to(torch.float8_e4m3fn)
+        s[e] = scale
+    return q, s
+
+
+def zipf_routing(M, E_, topk, seed):
+    """topk distinct experts per token from Zipf(s=1.2) over a seeded permutation of the expert ids, weights =
+    softmax of N(0,1) over the chosen experts (BASELINE.json's skewed-routing sweep)."""
+    g = torch.Generator().manual_seed(seed + 3)
+    perm = torch.randperm(E_, generator=g)
+    p = 1.0 / torch.arange(1, E_ + 1, dtype=torch.float64) ** 1.2
+    p = (p / p.sum()).to(torch.float32)
+    ranks = torch.multinomial(p.expand(M, E_), topk, replacement=False, generator=g)
+    ids = perm[ranks].to(torch.int32)
+    w = torch.softmax(torch.randn((M, topk), generator=g, dtype=torch.float32), dim=-1)
+    return w, ids
+
+
+def median_ms(fn, sync, steps=10, warmup=3):
+    return statistics.median(timed(fn, steps, warmup, sync))
+
+
+def bench_other_configs(dev, rank, world, sync, max_over_ranks, exchange, steps):
+    """Config 3 (Mixtral-8x7B shape, QuantType.per_Token, M=4096) and config 4 (Qwen3-235B-A22B shape, Zipf(1.2) routing,
+    M in {1, 16, 128, 1024, 16384}) through the same public calls; N > 1: expert parallel over the N ranks."""
+    import aiter_b200
+    from aiter_b200 import ep
+    QT = aiter_b200.QuantType
+    out = {}
+    # ---- config 3
+    Hm, Im, Em, Km, Mm = 4096, 14336, 8, 2, 4096
+    if Em % world == 0 and Mm % world == 0:
+        el = Em // world
+        w1_q, w1_s = quantise_weights_per_channel(el, 2 * Im, Hm, 11 + 1000 * rank, dev)
+        w2_q, w2_s = quantise_weights_per_channel(el, Hm, Im, 12 + 1000 * rank, dev)
+        g = torch.Generator().manual_seed(21)
+        x = torch.randn((Mm, Hm), generator=g, dtype=torch.float32).to(torch.bfloat16)
+        logits = torch.randn((Mm, Em), generator=g, dtype=torch.float32).to(dev)
+        tw, ti = aiter_b200.fused_topk(x.to(dev), logits, Km, True)
+        ml = Mm // world
+        rows = slice(rank * ml, (rank + 1) * ml)
+        dx, dtw, dti = x[rows].to(dev), tw[rows].contiguous(), ti[rows].contiguous()
+        if world == 1:
+            fn = lambda: aiter_b200.fused_moe(dx, w1_q, w2_q, dtw, dti, quant_type=QT.per_Token, w1_scale=w1_s, w2_scale=w2_s)
+        else:
+            fn = lambda: ep.ep_fused_moe(dx, w1_q, w2_q, dtw, dti, w1_s, w2_s, Em, exchange="nccl", quant_type=QT.per_Token)
+        ms = max_over_ranks(median_ms(fn, sync, steps))
+        out["cfg3_mixtral_per_token_M4096_H4096_I14336_E8_topk2"] = {
+            "ms_per_layer": ms, "tflops": 6.0 * Mm * Km * Hm * Im / (ms * 1e-3) / 1e12,
+            "parallelism": f"ep{world}" + (" (nccl exchange)" if world > 1 else "")}
+        del w1_q, w1_s, w2_q, w2_s
+        torch.cuda.empty_cache()
+    # ---- config 4
+    Hq, Iq, Eq, Kq = 4096, 1536, 128, 8
+    if Eq % world == 0:
+        el = Eq // world
+        w1_q, w1_s = quantise_weights(el, 2 * Iq, Hq, 31 + 1000 * rank, dev)
+        w2_q, w2_s = quantise_weights(el, Hq, Iq, 32 + 1000 * rank, dev)
+        sweep = {}
+        for Mq in (1, 16, 128, 1024, 16384):
+            if Mq % world != 0:
+                continue   # every rank owns the same number of rows
+            g = torch.Generator().manual_seed(Mq)
+            x = torch.randn((Mq, Hq), generator=g, dtype=torch.float32).to(torch.bfloat16)
+            tw, ti = zipf_routing(Mq, Eq, Kq, Mq)
+            ml = Mq // world
+            rows = slice(rank * ml, (rank + 1) * ml)
+            dx, dtw, dti = x[rows].to(dev), tw[rows].to(dev), ti[rows].to(dev)
+            if world == 1:
+                fn = lambda: aiter_b200.fused_moe(dx, w1_q, w2_q, dtw, dti, quant_type=QT.per_1x128, w1_scale=w1_s, w2_scale=w2_s)
+            else:
+                fn = lambda: ep.ep_fused_moe(dx, w1_q, w2_q, dtw, dti, w1_s, w2_s, Eq, exchange=exchange)
+            ms = max_over_ranks(median_ms(fn, sync, steps))
+            sweep[str(Mq)] = {"us_per_layer": ms * 1e3, "tflops": 6.0 * Mq * Kq * Hq * Iq / (ms * 1e-3) / 1e12}
+        out["cfg4_qwen3_zipf1.2_H4096_I1536_E128_topk8"] = {
+            "sweep_M": sweep, "parallelism": f"ep{world}" + (f" ({exchange} exchange)" if world > 1 else "")}
+        del w1_q, w1_s, w2_q, w2_s
+        torch.cuda.empty_cache()
+    aiter_b200.check_device_status()
+    return out
+
+
+def ep_parity_check(out_local, x, tw, ti, w, table, rank, world, dev, n_rows=4):
+    """N > 1: the first rows of rank 0's output against the CPU oracle. The experts those rows are routed to are
+    fetched from the ranks that own them (broadcasts, outside every timed region); the oracle then runs on rank 0."""
+    import torch.distributed as dist
+    w1_q, w1_s, w2_q, w2_s = w
+    rows_ids = ti[:n_rows]
+    needed = sorted(set(int(e) for e in rows_ids.flatten().tolist()))
+    owned = [torch.nonzero(table == r).flatten().tolist() for r in range(world)]
+    got = []
+    for gexp in needed:
+        owner = int(table[gexp])
+        li = owned[owner].index(gexp)
+        parts = []
+        for t in (w1_q, w1_s, w2_q, w2_s):
+            buf = t[li].contiguous() if rank == owner else torch.empty_like(t[0])
+            dist.broadcast(buf.view(torch.uint8), src=owner)   # as bytes: the collective need not know e4m3
+            if rank == 0:
+                parts.append(buf.cpu())
+        got.append(parts)
+    if rank != 0:
+        return None
+    from oracle import moe_oracle
+    remap = {gexp: i for i, gexp in enumerate(needed)}
+    ids = torch.tensor([[remap[int(e)] for e in row] for row in rows_ids.tolist()], dtype=torch.int32)
+    stack = lambda k: torch.stack([p[k] for p in got])
+    ref = moe_oracle.fused_moe_ref(x[:n_rows], stack(0), stack(1), stack(2), stack(3), tw[:n_rows], ids)
+    st = moe_oracle.error_stats(out_local[:n_rows].cpu(), ref)
+    keep = ("numel", "n_diff", "n_one_ulp", "max_abs_over_rms", "max_abs_excl_one_ulp_over_rms", "frac_within", "has_nan")
+    res = {k: st[k] for k in keep}
+    res["rows"] = n_rows
+    res["experts_fetched"] = len(needed)
+    res["ok"] = bool((not st["has_nan"]) and st["frac_within"] >= 0.995 and st["max_abs_excl_one_ulp_over_rms"] <= 0.02
+                     and st["max_abs_over_rms"] <= 0.04)
+    return res
+
+
 def emit(line):
     """The one JSON line goes to the real stdout; everything else this process (or a library such as NCCL,
     which prints a version banner) writes to stdout has been pointed at stderr."""
@@ -322,23 +464,28 @@ def main():
     ap.add_argument("--tokens", type=int, default=M_PREFILL, help="override M (profiling a small case)")
     ap.add_argument("--experts", type=int, default=E, help="override E (profiling a small case)")
     ap.add_argument("--skip-decode", action="store_true")
+    ap.add_argument("--skip-other-configs", action="store_true", help="leave out configs 3 and 4 (other_configs)")
     ap.add_argument("--ep-exchange", default="auto", choices=["auto", "nccl", "p2p"],
                     help="N>1: NCCL all-gather + fp32 reduce-scatter, or dispatch/combine over peer memory; auto = "
                          "peer memory if every rank can map its peers' buffers, else NCCL")
+    ap.add_argument("--ep-placement", default="balanced", choices=["contiguous", "balanced"],
+                    help="N>1: experts in contiguous slices per rank, or placed by the route counts of a calibration "
+                         "batch (other seed) so that every rank gets the same number of experts and a level load")
     ap.add_argument("--cuda-profiler-range", action="store_true",
                     help="bracket the device-timed steps with cudaProfilerStart/Stop (ncu --profile-from-start off)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
     args.warmup = max(args.warmup, 3)
-    if args.tokens != M_PREFILL or args.experts != E:
+    small = args.tokens != M_PREFILL or args.experts != E
+    if small:
         M_PREFILL, E = args.tokens, args.experts
         WORKLOAD = f"small_case_M{M_PREFILL}_H{H}_I{I}_E{E}_topk{TOPK} (not the headline workload)"
 
     import importlib
     import torch.distributed as dist
     import aiter_b200
-    from aiter_b200 import ep
+    from aiter_b200 import _lib, ep
     fm = importlib.import_module("aiter_b200.fused_moe")
     QT = aiter_b200.QuantType
 
@@ -357,6 +504,12 @@ def main():
             dist.barrier()
             torch.cuda.synchronize()
 
+    def max_over_ranks(v):
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     w1_q, w1_s, w2_q, w2_s = make_layer(dev, rank, world)
     x, tw, ti = make_tokens(M_PREFILL, device=dev)
     m_local = M_PREFILL // world
@@ -367,6 +520,22 @@ def main():
     hout2 = [hout, torch.empty((m_local, H), dtype=torch.bfloat16).pin_memory()]
     dx, dtw, dti = hx.to(dev), htw.to(dev), hti.to(dev)
 
+    # expert -> rank table: contiguous slices, or levelled by the route counts of a calibration batch (another seed),
+    # as a loader would place experts from routing statistics; rank r holds its experts in ascending global id
+    table = torch.arange(E, dtype=torch.int32) // (E // world)
+    placement_info = None
+    if world > 1 and args.ep_placement == "balanced":
+        _xc, _twc, tic = make_tokens(M_PREFILL, seed=100, device=dev)
+        table = ep.balanced_expert_placement(torch.bincount(tic.flatten().long(), minlength=E), world)
+    if world > 1:
+        counts = torch.bincount(ti.flatten().long(), minlength=E)
+        load = torch.zeros(world, dtype=torch.long).index_add_(0, table.long(), counts)
+        ranks_per_token = torch.zeros((M_PREFILL, world), dtype=torch.bool).scatter_(1, table[ti.long()].long(), True).sum(1)
+        placement_info = {"kind": args.ep_placement, "routes_per_rank": load.tolist(),
+                          "max_over_mean": float(load.max()) / (float(load.sum()) / world),
+                          "mean_ranks_per_token": float(ranks_per_token.float().mean())}
+    xr = table.to(dev) if (world > 1 and args.ep_placement == "balanced") else None
+
     exchange = args.ep_exchange
     if world > 1 and exchange == "auto":
         try:
@@ -376,18 +545,14 @@ def main():
             print(f"[bench] peer-memory exchange not available ({e}); using NCCL", file=sys.stderr)
             exchange = "nccl"
     if world == 1:
-        def step_dev():
-            return aiter_b200.fused_moe(dx, w1_q, w2_q, dtw, dti, quant_type=QT.per_1x128,
-                                        w1_scale=w1_s, w2_scale=w2_s)
-
         def layer(a, b, c):
             return aiter_b200.fused_moe(a, w1_q, w2_q, b, c, quant_type=QT.per_1x128, w1_scale=w1_s, w2_scale=w2_s)
     else:
-        def step_dev():
-            return ep.ep_fused_moe(dx, w1_q, w2_q, dtw, dti, w1_s, w2_s, E, exchange=exchange)
-
         def layer(a, b, c):
-            return ep.ep_fused_moe(a, w1_q, w2_q, b, c, w1_s, w2_s, E, exchange=exchange)
+            return ep.ep_fused_moe(a, w1_q, w2_q, b, c, w1_s, w2_s, E, exchange=exchange, expert_rank=xr)
+
+    def step_dev():
+        return layer(dx, dtw, dti)
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -397,14 +562,11 @@ def main():
     t_dev = timed(step_dev, args.steps, args.warmup, sync, profile=args.cuda_profiler_range)
     stage_marks, fm.kernel_bench_events = fm.kernel_bench_events, None
     t_e2e_total = timed_e2e_pipelined(layer, (hx, htw, hti), hout2, dev, args.steps, min(args.warmup, 3), sync)
+    launches0 = _lib.launch_count
+    step_dev()
+    gpu_launches = (_lib.launch_count - launches0) * args.steps * 2   # device-timed and end-to-end loops
     clocks = sampler.stop() if rank == 0 else None
     aiter_b200.check_device_status()
-
-    def max_over_ranks(ms_total):
-        t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
 
     ms_step = max_over_ranks(sum(t_dev)) / args.steps
     ms_e2e = max_over_ranks(t_e2e_total) / args.steps
@@ -418,14 +580,18 @@ def main():
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate, bf16 in/out)", "data": "synthetic",
         "config": {"workload": WORKLOAD, "tokens": M_PREFILL, "model_dim": H, "inter_dim": I, "experts": E,
-                   "topk": TOPK, "parallelism": f"ep{world}" + (f" ({exchange} exchange)" if world > 1 else ""), "l2_policy": "inputs larger than L2 (11.3 GB of weights per step)"},
+                   "topk": TOPK, "parallelism": f"ep{world}" + (f" ({exchange} exchange, {args.ep_placement} expert placement)" if world > 1 else ""),
+                   "l2_policy": "inputs larger than L2 (11.3 GB of weights per step)"},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": int(hx.numel() * 2 + htw.numel() * 4 + hti.numel() * 4) * world,
                 "d2h_bytes_per_step": int(hout.numel() * 2) * world,
                 "how": "pinned host -> device copy of x, topk_weight, topk_ids and device -> pinned host copy of the bf16 "
                        "result every step, on two copy streams overlapping the neighbouring steps' compute"},
         "clocks": clocks,
+        "gpu_launches": gpu_launches,   # kernels of this library launched by this rank inside the two timed loops
     }
+    if placement_info is not None:
+        line["expert_placement"] = placement_info
 
     if world == 1:
         # per-kernel device time averaged over the timed steps themselves (events recorded inside the timed loop)
@@ -436,16 +602,14 @@ def main():
             for (n0, e0), (_n1, e1) in zip(marks[:-1], marks[1:]):
                 kb_acc.setdefault(n0, []).append(e0.elapsed_time(e1))
         kb = {k: sum(v) / len(v) for k, v in kb_acc.items()}
-        n_sort = 3 if M_PREFILL * TOPK > 16384 else 1
-        line["gpu_launches"] = (n_sort + 4) * args.steps * 2   # device-timed and e2e loops
         line["kernels_ms"] = {k: round(v, 4) for k, v in kb.items()}
         s1 = 4.0 * M_PREFILL * TOPK * H * I / (kb["stage1"] * 1e-3) / 1e12
         s2 = 2.0 * M_PREFILL * TOPK * H * I / (kb["stage2"] * 1e-3) / 1e12
-        line["roofline"] = {"bound": "tensor", "kernel": "moe_gemm_kernel<1> (stage 1)", "achieved": s1,
+        line["roofline"] = {"bound": "tensor", "kernel": "stage-1 GEMM (gate/up + SiLU*up + requant)", "achieved": s1,
                             "peak": fp8_peak, "unit": "TFLOP/s", "frac": s1 / fp8_peak,
-                            # DRAM bytes of one stage-1 launch: ncu capture of the M=1024, E=32 case (1.172 GB)
-                            # scaled by the expert count (profiles/moe_gemm_kernel_small_case_M1024_E32_full.md)
-                            "traffic": 1.172e9 * E / 32 if M_PREFILL == 8192 else None,
+                            "traffic": STAGE1_DRAM_BYTES_PER_EXPERT * E if M_PREFILL == 8192 else None,
+                            "traffic_source": "extrapolated: " + STAGE1_DRAM_CAPTURE + ", scaled by the expert count",
+                            "algorithmic_bytes": 2 * E * I * H + M_PREFILL * H + M_PREFILL * TOPK * I,
                             "peak_source": f"2 x bf16_tflops of {pk['source']} ({pk['bf16_tflops']} TFLOP/s burst); "
                                            "the driver's peak file has no FP8 entry",
                             "stage2_achieved": s2, "stage2_frac": s2 / fp8_peak}
@@ -454,57 +618,28 @@ def main():
         if lib is not None:
             line["roofline"]["library_fp8_gemm_tflops"] = lib
             line["roofline"]["frac_of_library_fp8_gemm"] = s1 / lib
-    if world == 1 and not args.skip_decode:
-        # ---- decode case (M=64): HBM-bound weight streaming
-        xd, twd, tid = make_tokens(M_DECODE, seed=1, device=dev)
-        dxd, dtwd, dtid = xd.to(dev), twd.to(dev), tid.to(dev)
-        n_act = int(torch.unique(tid).numel())
-
-        def step_decode():
-            return aiter_b200.fused_moe(dxd, w1_q, w2_q, dtwd, dtid, quant_type=QT.per_1x128, w1_scale=w1_s, w2_scale=w2_s)
-
-        td = timed(step_decode, max(args.steps, 20), args.warmup, sync)
-        us = statistics.median(td) * 1e3
-        gbs = algorithmic_bytes(M_DECODE, n_act) / (us * 1e-6) / 1e9
-        kbd = kernel_breakdown(fm, (dxd, w1_q, w2_q, dtwd, dtid, None, w1_s, w2_s, None, None, torch.bfloat16))
-        # the same layer replayed from a CUDA graph (how serving stacks run decode): no launch gaps
-        graph = torch.cuda.CUDAGraph()
-        side = torch.cuda.Stream(dev)
-        side.wait_stream(torch.cuda.current_stream(dev))
-        with torch.cuda.stream(side):
-            step_decode()
-        torch.cuda.current_stream(dev).wait_stream(side)
-        with torch.cuda.graph(graph):
-            step_decode()
-        tg = timed(graph.replay, max(args.steps, 20), args.warmup, sync)
-        us_graph = statistics.median(tg) * 1e3
-        line["decode"] = {"metric": "DSV3 FP8-blockscale fused_moe us/layer (M=64)", "value": us, "unit": "us",
-                          "graph_replay_us": us_graph,
-                          "graph_replay_frac_of_hbm": algorithmic_bytes(M_DECODE, n_act) / (us_graph * 1e-6) / 1e9 / pk["hbm_gbs"],
-                          "active_experts": n_act, "kernels_ms": {k: round(v, 4) for k, v in kbd.items()},
-                          "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                                       "frac": gbs / pk["hbm_gbs"], "traffic": None,
-                                       "peak_source": f"hbm_gbs of {pk['source']}"}}
-        aiter_b200.check_device_status()
-    if world == 1 and not args.no_cpu_baseline:
-        cb = cpu_baseline(n_exp=64)
-        line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
     if world > 1:
-        line["gpu_launches"] = (3 + 4) * args.steps * 2
         accb = {}
         for _ in range(5):
             timers = []
-            ep.ep_fused_moe(dx, w1_q, w2_q, dtw, dti, w1_s, w2_s, E, timers=timers, exchange=exchange)
+            ep.ep_fused_moe(dx, w1_q, w2_q, dtw, dti, w1_s, w2_s, E, timers=timers, exchange=exchange, expert_rank=xr)
             sync()
             for (n0, e0), (_n1, e1) in zip(timers[:-1], timers[1:]):
                 accb.setdefault(n0, []).append(e0.elapsed_time(e1))
         line["ep_breakdown_ms_rank0"] = {k: round(sum(v) / len(v), 4) for k, v in accb.items()}
-        line["gpu_launches"] = ((3 + 4) + (3 if exchange == "p2p" else 0)) * args.steps * 2
+        # host time of one layer call (launches only, no synchronisation): what bounds the step when the device is faster
+        torch.cuda.synchronize()
+        th = []
+        for _ in range(5):
+            t0 = time.perf_counter()
+            step_dev()
+            th.append((time.perf_counter() - t0) * 1e3)
+            torch.cuda.synchronize()
+        line["host_ms_per_call_rank0"] = round(statistics.median(th), 4)
         # Roofline of the sharded layer: the slower of (this rank's share of the flops at the FP8 peak) and (the bytes
         # that must cross NVLink per rank at the measured 770 GB/s per direction); achieved = the step time.
-        epr = E // world
         touched = torch.zeros((M_PREFILL, world), dtype=torch.bool)
-        touched.scatter_(1, (ti // epr).long(), True)                       # [token, rank]: a route on that rank
+        touched.scatter_(1, table[ti.long()].long(), True)                  # [token, rank]: a route on that rank
         owner = torch.arange(M_PREFILL) // m_local
         remote = touched.clone()
         remote[torch.arange(M_PREFILL), owner] = False                      # rows that leave the owning rank
@@ -522,11 +657,63 @@ def main():
                             "traffic": None, "nvlink_bytes_rank0": int(disp + comb),
                             "target_ms": {"flops_at_fp8_peak": t_flops, "nvlink_at_770GBs": t_link},
                             "peak_source": f"2 x bf16_tflops of {pk['source']}; NVLink: 770 GB/s per direction measured on this pool"}
+        # numerical check of the path that was just timed (outside the timed region)
+        out_chk = step_dev()
+        torch.cuda.synchronize()
+        line["parity_check"] = ep_parity_check(out_chk, x[rows], tw[rows], ti[rows], (w1_q, w1_s, w2_q, w2_s), table, rank,
+                                               world, dev)
+
+    if not args.skip_decode and not small and M_DECODE % world == 0:
+        # ---- decode case (M=64): HBM-bound weight streaming; N > 1: the same expert-parallel path, 64/N rows per rank
+        xd, twd, tid = make_tokens(M_DECODE, seed=1, device=dev)
+        md = M_DECODE // world
+        rd = slice(rank * md, (rank + 1) * md)
+        dxd, dtwd, dtid = xd[rd].to(dev), twd[rd].to(dev), tid[rd].to(dev)
+        act_per_rank = [int(torch.unique(tid[table[tid.long()] == r]).numel()) for r in range(world)]
+        n_act = int(torch.unique(tid).numel())
+
+        def step_decode():
+            return layer(dxd, dtwd, dtid)
+
+        td = timed(step_decode, max(args.steps, 20), args.warmup, sync)
+        us = max_over_ranks(statistics.median(td) * 1e3)
+        # bytes the busiest rank must stream: its active experts' weights (+ activations, negligible)
+        gbs = algorithmic_bytes(M_DECODE, max(act_per_rank)) / (us * 1e-6) / 1e9
+        dec = {"metric": "DSV3 FP8-blockscale fused_moe us/layer (M=64)", "value": us, "unit": "us",
+               "active_experts": n_act, "active_experts_per_rank": act_per_rank,
+               "roofline": {"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s (busiest rank)",
+                            "frac": gbs / pk["hbm_gbs"], "traffic": None, "peak_source": f"hbm_gbs of {pk['source']}"}}
+        if world == 1:
+            kbd = kernel_breakdown(fm, (dxd, w1_q, w2_q, dtwd, dtid, None, w1_s, w2_s, None, None, torch.bfloat16))
+            dec["kernels_ms"] = {k: round(v, 4) for k, v in kbd.items()}
+            # the same layer replayed from a CUDA graph (how serving stacks run decode): no launch gaps
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream(dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                step_decode()
+            torch.cuda.current_stream(dev).wait_stream(side)
+            with torch.cuda.graph(graph):
+                step_decode()
+            tg = timed(graph.replay, max(args.steps, 20), args.warmup, sync)
+            us_graph = statistics.median(tg) * 1e3
+            dec["graph_replay_us"] = us_graph
+            dec["graph_replay_frac_of_hbm"] = algorithmic_bytes(M_DECODE, n_act) / (us_graph * 1e-6) / 1e9 / pk["hbm_gbs"]
+        line["decode"] = dec
+        aiter_b200.check_device_status()
+    if world == 1 and not args.no_cpu_baseline:
+        cb = cpu_baseline(n_exp=64)
+        line["cpu_baseline"] = {k: cb[k] for k in ("value", "unit", "cores", "kind", "sample")}
+    if not args.skip_other_configs and not small:
+        del w1_q, w1_s, w2_q, w2_s
+        torch.cuda.empty_cache()
+        line["other_configs"] = bench_other_configs(dev, rank, world, sync, max_over_ranks, exchange, min(args.steps, 10))
 
     if rank == 0:
         emit(line)
     if world > 1:
         dist.barrier()
+        ep.PeerExchange.clear()
         dist.destroy_process_group()
 
 

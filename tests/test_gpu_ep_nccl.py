@@ -53,6 +53,8 @@ def _worker(rank, world, port, ret):
         aiter_b200.check_device_status()
         ret[rank] = out.cpu()
         ret[rank + world] = outp.cpu()
+        dist.barrier()
+        ep.PeerExchange.clear()   # unmap the peers' arenas while the group still exists
     finally:
         dist.destroy_process_group()
 
