@@ -57,6 +57,7 @@ _SIGNATURES = {
     "b200_ep_ipc_export": (ctypes.c_int, [_T, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64)]),
     "b200_ep_ipc_open": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_int64)]),
     "b200_ep_ipc_close": (ctypes.c_int, [ctypes.c_int64, ctypes.c_int]),
+    "b200_moe_debug_config": (ctypes.c_int, [ctypes.c_int64, ctypes.c_int]),
 }
 
 _lib = None

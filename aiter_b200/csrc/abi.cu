@@ -32,6 +32,8 @@ void launch_moe_stage2(const aiter_tensor_t*, const aiter_tensor_t*, const aiter
                        const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*,
                        aiter_tensor_t*, aiter_tensor_t*, int, int, int, int, int, cudaStream_t);
 
+void set_gemm_debug(long long, int);
+
 void launch_biased_grouped_topk(const aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*, int, int,
                                 int, float, cudaStream_t);
 void launch_topk_softmax(aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*, const aiter_tensor_t*, int, cudaStream_t);
@@ -191,6 +193,14 @@ B200_EXPORT int b200_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* 
         launch_moe_stage2(a2, a2_scale, w2, w2_scale, sorted_token_ids, sorted_weights, sorted_expert_ids,
                           num_valid_ids, acc, status, col_begin, col_end, sm_margin, quant_type, doweight, (cudaStream_t)stream);
     });
+}
+
+// Self-test of the bounded device-side waits: sets, for every later GEMM launch of this process, the wait limit in SM
+// clocks (<= 0: the built-in ~2 s) and whether the weight producer loads nothing. With the producer stalled no copy or
+// MMA is ever in flight, so the waits simply run out: every CTA winds down, frees its tensor memory and sets the
+// caller's status word. Not for production use.
+B200_EXPORT int b200_moe_debug_config(int64_t wait_limit_cycles, int stall_weight_producer) {
+    return safe_call([&] { set_gemm_debug((long long)wait_limit_cycles, stall_weight_producer); });
 }
 
 B200_EXPORT int b200_biased_grouped_topk(const aiter_tensor_t* gating_output, const aiter_tensor_t* correction_bias,

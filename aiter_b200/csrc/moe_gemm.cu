@@ -86,6 +86,8 @@ struct GemmParams {
     float* acc;              // stage 2 out [M, H] fp32
     int* status;
     int use_weight;          // multiply this stage's GEMM result by the route weight (sorted_w)
+    long long wait_limit;    // SM clocks after which a device-side wait gives up (sets status, the CTA winds down)
+    int stall_producer;      // self-test only: the weight producer loads nothing, so every wait downstream runs out
 };
 
 // torch: silu(x) = x / (1 + exp(-x)) in fp32, then * up (aiter/fused_moe.py:3676).
@@ -209,14 +211,14 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                 }
             };
             uint32_t it = 0;
-            bool ok = true;
+            bool ok = !p.stall_producer;   // self-test: issue nothing; the other roles' waits then run out
             for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
                 int r0, r1;
                 tile_rows(t, r0, r1);
                 for (int kb = 0; kb < p.KB; ++kb, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1u;
-                    if (!(ok = ptx::mbar_wait<kTmaSleepNs>(empty_bar(s), ph ^ 1u, abort_flag))) break;
+                    if (!(ok = ptx::mbar_wait<kTmaSleepNs>(empty_bar(s), ph ^ 1u, abort_flag, p.wait_limit))) break;
                     ptx::mbar_arrive_expect_tx(full_bar(s), kBBytes);
                     ptx::tma_load_2d(sB + s * kBBytes, &tmap_w, kb * BK, r0, full_bar(s));
                     ptx::tma_load_2d(sB + s * kBBytes + kBBytes / 2, &tmap_w, kb * BK, r1, full_bar(s));
@@ -238,8 +240,8 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                     const int ts = tcount & 1;
                     const uint32_t tph = (tcount >> 1) & 1u;
                     if (!PT || kb == 0)
-                        if (!(ok = ptx::mbar_wait(tempty_bar(ts), tph ^ 1u, abort_flag))) break;
-                    if (!(ok = ptx::mbar_wait(full_bar(s), ph, abort_flag))) break;
+                        if (!(ok = ptx::mbar_wait(tempty_bar(ts), tph ^ 1u, abort_flag, p.wait_limit))) break;
+                    if (!(ok = ptx::mbar_wait(full_bar(s), ph, abort_flag, p.wait_limit))) break;
                     // the activation rows were written by cp.async (generic proxy); order them
                     // before the tensor core's async-proxy reads
                     ptx::fence_proxy_async();
@@ -302,7 +304,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
             for (int kb = 0; kb < p.KB; ++kb, ++it) {
                 const int s = it % kStages;
                 const uint32_t ph = (it / kStages) & 1u;
-                if (!(ok = ptx::mbar_wait<kProducerSleepNs>(empty_bar(s), ph ^ 1u, abort_flag))) break;
+                if (!(ok = ptx::mbar_wait<kProducerSleepNs>(empty_bar(s), ph ^ 1u, abort_flag, p.wait_limit))) break;
                 const uint32_t dst = sA + s * kABytes;
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
@@ -375,7 +377,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
             for (int kb = PT ? p.KB - 1 : 0; kb < p.KB; ++kb, ++it) {
                 const int ts = it & 1;
                 const uint32_t tph = (it >> 1) & 1u;
-                if (!(ok = ptx::mbar_wait<kEpilogueSleepNs>(tfull_bar(ts), tph, abort_flag))) break;
+                if (!(ok = ptx::mbar_wait<kEpilogueSleepNs>(tfull_bar(ts), tph, abort_flag, p.wait_limit))) break;
                 ptx::tc_fence_after();
                 const float sa = pf_a * wgt;   // wgt is exactly 1 when the stage does not weight
                 const float s0 = PT ? sa : sa * pf_w0, s1 = PT ? sa : sa * pf_w1;
@@ -584,6 +586,11 @@ CUtensorMap make_weight_map(const void* ptr, uint64_t rows, uint64_t K) {
     return m;
 }
 
+// Process-wide settings of the wait self-test (b200_moe_debug_config): the limit of every device-side wait in SM
+// clocks, and whether the weight producer is stalled. Defaults: the built-in limit, no stall.
+long long g_wait_limit = ptx::kWaitLimitCycles;
+int g_stall_producer = 0;
+
 template <int STAGE, bool PT, int ACT = 0>
 void launch_gemm(const CUtensorMap& tmap, const GemmParams& p, int64_t max_tiles, int dev, cudaStream_t stream,
                  int sm_margin = 0) {
@@ -593,14 +600,24 @@ void launch_gemm(const CUtensorMap& tmap, const GemmParams& p, int64_t max_tiles
                                        kSmemBytes));
         if (dev < 64) attr_set[dev] = true;
     }
+    B200_CHECK(sm_margin < sm_count(dev), "sm_margin (", sm_margin, ") must leave at least one of the device's ",
+               sm_count(dev), " SMs to the kernel");
     int64_t grid = sm_count(dev) - sm_margin;   // SMs left free for a collective running beside this kernel
     if (max_tiles < grid) grid = max_tiles;
     if (grid < 1) return;
-    moe_gemm_kernel<STAGE, PT, ACT><<<(unsigned)grid, kThreads, kSmemBytes, stream>>>(tmap, p);
+    GemmParams q = p;
+    q.wait_limit = g_wait_limit;
+    q.stall_producer = g_stall_producer;
+    moe_gemm_kernel<STAGE, PT, ACT><<<(unsigned)grid, kThreads, kSmemBytes, stream>>>(tmap, q);
     B200_CUDA(cudaGetLastError());
 }
 
 }  // namespace
+
+void set_gemm_debug(long long wait_limit_cycles, int stall_producer) {
+    g_wait_limit = wait_limit_cycles > 0 ? wait_limit_cycles : ptx::kWaitLimitCycles;
+    g_stall_producer = stall_producer != 0;
+}
 
 void launch_moe_stage1(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale, const aiter_tensor_t* w1,
                        const aiter_tensor_t* w1_scale, const aiter_tensor_t* sorted_ids,
@@ -646,6 +663,8 @@ void launch_moe_stage1(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale,
                "a2 must have at least as many rows as sorted_token_ids (", sorted_ids->numel_, "), has ", P);
     if (!pt) B200_CHECK((int64_t)a2_scale->numel_ >= P * (I / 128), "a2_scale must have P*inter_dim/128 elements");
     B200_CHECK(num_valid->numel_ >= 2 && status->numel_ >= 1, "num_valid_ids needs 2 and status 1 element");
+    B200_CHECK((int64_t)sorted_eids->numel_ * BM >= (int64_t)sorted_ids->numel_ - (BM - 1),
+               "sorted_expert_ids must hold one entry per 128 sorted rows (was the sort run with unit_size 128?)");
     B200_CHECK(E * N2 < ((int64_t)1 << 31) && M < (1 << 24), "problem too large");
     B200_CHECK(((uintptr_t)a1->ptr & 15) == 0 && ((uintptr_t)w1->ptr & 15) == 0 && ((uintptr_t)a2->ptr & 15) == 0 &&
                    ((uintptr_t)w1_scale->ptr & 15) == 0,
@@ -705,7 +724,7 @@ void launch_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* a2_scale,
                "column range [", col_begin, ", ", col_end, ") must lie in [0, model_dim] on 256-column boundaries");
     B200_CHECK(acc->shape[1] == col_end - col_begin, "acc must be [M, col_end - col_begin]");
     B200_CHECK(((uintptr_t)acc->ptr & 15) == 0, "acc must be 16-byte aligned (bulk reductions)");
-    B200_CHECK(sm_margin >= 0 && sm_margin < 128, "sm_margin must be in [0, 128)");
+    B200_CHECK(sm_margin >= 0, "sm_margin must not be negative");
     B200_CHECK(I % 128 == 0 && H % 128 == 0, "inter_dim and model_dim must be multiples of 128");
     if (pt) {
         B200_CHECK((int64_t)a2_scale->numel_ >= P, "a2_scale must have one element per sorted row for per_Token");
@@ -719,6 +738,8 @@ void launch_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* a2_scale,
     B200_CHECK(P >= (int64_t)sorted_ids->numel_ && sorted_w->numel_ >= sorted_ids->numel_,
                "a2 and sorted_weights must cover sorted_token_ids");
     B200_CHECK(num_valid->numel_ >= 2 && status->numel_ >= 1, "num_valid_ids needs 2 and status 1 element");
+    B200_CHECK((int64_t)sorted_eids->numel_ * BM >= (int64_t)sorted_ids->numel_ - (BM - 1),
+               "sorted_expert_ids must hold one entry per 128 sorted rows (was the sort run with unit_size 128?)");
     B200_CHECK(E * H < ((int64_t)1 << 31) && M < (1 << 24), "problem too large");
     B200_CHECK(((uintptr_t)a2->ptr & 15) == 0 && ((uintptr_t)w2->ptr & 15) == 0 && ((uintptr_t)acc->ptr & 15) == 0,
                "a2, w2 and acc must be 16-byte aligned");

@@ -42,21 +42,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-constexpr long long kWaitLimitCycles = 4000000000LL;  // about 2 s at 1.9 GHz
+constexpr long long kWaitLimitCycles = 4000000000LL;  // default limit of a wait: about 2 s at 1.9 GHz
 
-// Returns false if the wait ran out.  A waiter gives up only on its own clock, never because
-// another thread did: all waiters of one barrier phase then take the same way out, which keeps
-// thread groups that later meet at a hardware barrier together.
+// Returns false if the wait ran out (after `limit` SM clocks).  A waiter gives up only on its own
+// clock, never because another thread did: all waiters of one barrier phase then take the same way
+// out, which keeps thread groups that later meet at a hardware barrier together.
 // SLEEP_NS > 0 backs off with nanosleep between polls: a polling warp otherwise takes issue
 // slots from the warps of its SM sub-partition that do the arithmetic.
 template <int SLEEP_NS = 0>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          long long limit = kWaitLimitCycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if (SLEEP_NS > 0) __nanosleep(SLEEP_NS);
-        if ((++spins & 0xffu) == 0 && clock64() - t0 > kWaitLimitCycles) {
+        if ((++spins & 0x3fu) == 0 && clock64() - t0 > limit) {
             *abort_flag = 1;
             return false;
         }

@@ -215,6 +215,41 @@ def _check_unsupported(**kw):
                                       "FP8 block-scale path")
 
 
+def _fold_shared_expert(w1, w2, w1_scale, w2_scale, shared, shared_expert_id, quant_type, expert_mask):
+    """Separate shared-expert weights (the ``shared_*`` arguments of aiter/fused_moe.py:488-493).
+
+    The calling contract is the reference's (aiter/fhmoe.py:36-47, 74-98): all four tensors together, the routed
+    weights carry a dummy final row, ``shared_expert_id == E - 1``, ``shared_w1 [1, 2I, H]`` / ``shared_w2 [1, H, I]``
+    in e4m3, no expert mask. The reference runs that row through a second weight format (MXFP4 routed + FP8 shared,
+    per_1x32 only); here routed and shared experts have the same FP8 block-scale format, so the shared weights are
+    copied into the dummy row (four device copies, stream-ordered before the layer) and the row is routed like
+    any other expert."""
+    if any(t is None for t in shared):
+        raise ValueError("shared_w1, shared_w2, shared_w1_scale, and shared_w2_scale must be provided together")
+    if quant_type != QuantType.per_1x128:
+        raise NotImplementedError("fused_moe: shared_w1/shared_w2 are supported with QuantType.per_1x128 / per_128x128 only")
+    if expert_mask is not None:
+        raise NotImplementedError("fused_moe: shared expert weights with an expert mask are not supported")
+    shared_w1, shared_w2, shared_w1_scale, shared_w2_scale = shared
+    E = w1.shape[0]
+    if shared_expert_id != E - 1:
+        raise ValueError("shared expert weights need a dummy final routed weight row and shared_expert_id == E - 1; "
+                         f"got {shared_expert_id=} and E={E}")
+    if shared_w1.dtype != dtypes.fp8 or shared_w2.dtype != dtypes.fp8:
+        raise ValueError("shared weights must use FP8 E4M3")
+    if tuple(shared_w1.shape) != (1, *w1.shape[1:]) or tuple(shared_w2.shape) != (1, *w2.shape[1:]):
+        raise ValueError(f"Expected shared_w1 shape {(1, *w1.shape[1:])} and shared_w2 shape {(1, *w2.shape[1:])}, got "
+                         f"{tuple(shared_w1.shape)} and {tuple(shared_w2.shape)}")
+    for dst, src, name in ((w1, shared_w1, "w1"), (w2, shared_w2, "w2"), (w1_scale, shared_w1_scale, "w1_scale"),
+                           (w2_scale, shared_w2_scale, "w2_scale")):
+        if not dst.is_contiguous():
+            raise ValueError(f"fused_moe: {name} must be contiguous to receive the shared expert's row")
+        row = dst.view(E, -1)[E - 1]
+        if src.numel() != row.numel():
+            raise ValueError(f"shared_{name} has {src.numel()} elements, one expert's {name} has {row.numel()}")
+        row.view(torch.uint8).copy_(src.contiguous().view(-1).view(torch.uint8))
+
+
 def get_inter_dim(w1_shape, w2_shape):
     """aiter/fused_moe.py:448-456."""
     E, _, model_dim = w1_shape
@@ -392,10 +427,7 @@ def fused_moe(
         a2_scale=(a2_scale, None),
         hidden_pad=(hidden_pad, 0), intermediate_pad=(intermediate_pad, 0), bias1=(bias1, None),
         bias2=(bias2, None), splitk=(splitk or 0, 0), swiglu_limit=(swiglu_limit, None),
-        beta=(beta, None), linear_beta=(linear_beta, None), shared_w1=(shared_w1, None),
-        shared_w2=(shared_w2, None), shared_w1_scale=(shared_w1_scale, None),
-        shared_w2_scale=(shared_w2_scale, None), shared_expert_id=(shared_expert_id, -1),
-        stage2_scatter=(stage2_scatter, None))
+        beta=(beta, None), linear_beta=(linear_beta, None), stage2_scatter=(stage2_scatter, None))
     if gate_mode not in (None, "separated"):
         raise NotImplementedError(f"fused_moe: gate_mode={gate_mode!r} is not supported (separated only)")
     if not hidden_states.is_cuda:
@@ -435,6 +467,9 @@ def fused_moe(
         # one scale per expert -> one per output channel, the layout the per_Token kernels read
         w1_scale = w1_scale.to(dtypes.fp32).reshape(E, 1).expand(E, 2 * inter_dim)
         w2_scale = w2_scale.to(dtypes.fp32).reshape(E, 1).expand(E, model_dim)
+    shared = (shared_w1, shared_w2, shared_w1_scale, shared_w2_scale)
+    if any(t is not None for t in shared) or shared_expert_id != -1:
+        _fold_shared_expert(w1, w2, w1_scale, w2_scale, shared, shared_expert_id, quant_type, expert_mask)
     if M == 0:   # nothing to compute: the reference allocates the same empty result (aiter/fused_moe.py:579-619)
         return torch.empty((0, model_dim), dtype=dtype, device=hidden_states.device)
     return fused_moe_stages(hidden_states, w1.contiguous(), w2.contiguous(), topk_weight, topk_ids,

@@ -211,6 +211,13 @@ int b200_ep_ipc_export(const aiter_tensor_t* tensor, void* handle_out, int64_t* 
 int b200_ep_ipc_open(const void* handle, int device, int64_t* ptr_out);
 int b200_ep_ipc_close(int64_t ptr, int device);
 
+/* No counterpart in the reference (its kernels wait without a limit). Self-test hook of the bounded device-side
+ * waits of the GEMM kernels: for every later stage-1/stage-2 launch of this process, wait_limit_cycles is the number
+ * of SM clocks after which a wait gives up (<= 0 restores the built-in limit of about 2 s) and a non-zero
+ * stall_weight_producer makes the weight-loading role issue nothing. With it stalled nothing is in flight, the waits run
+ * out, every CTA winds down and frees its tensor memory, and the caller's status word is set to 1. Tests only. */
+int b200_moe_debug_config(int64_t wait_limit_cycles, int stall_weight_producer);
+
 /* DeepSeek-V3 style router: sigmoid scores, correction bias for the choice only, groups ranked by the sum
  * of their two best biased scores, top `topk_group` groups kept, top-k experts among them; weights are the
  * un-biased scores, renormalised when asked, times routed_scaling_factor. Replaces biased_grouped_topk

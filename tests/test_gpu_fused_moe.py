@@ -214,6 +214,36 @@ def dsv3_layer():
     torch.cuda.empty_cache()
 
 
+def test_separate_shared_expert_weights():
+    """The ``shared_*`` arguments (aiter/fused_moe.py:488-493; contract of aiter/fhmoe.py:36-98): routed weights with a
+    dummy final row, the shared expert's FP8 weights passed on their own, shared_expert_id == E - 1. The result is the
+    layer in which that row holds the shared weights."""
+    M, H, I, E, topk = 64, 512, 256, 5, 2           # experts 0..3 routed, row 4 = shared
+    g = torch.Generator().manual_seed(41)
+    x = torch.randn((M, H), generator=g).to(torch.bfloat16)
+    w1_q, w1_s = inputs.make_weights(E, 2 * I, H, seed=51)
+    w2_q, w2_s = inputs.make_weights(E, H, I, seed=52)
+    tw, ti = inputs.make_routing("softmax", M, E - 1, topk, seed=7)
+    ti = torch.cat([ti, torch.full((M, 1), E - 1, dtype=torch.int32)], dim=1)
+    tw = torch.cat([tw, torch.ones((M, 1), dtype=torch.float32)], dim=1)
+    ref = moe_oracle.fused_moe_ref(x, w1_q, w1_s, w2_q, w2_s, tw, ti)
+    d = to_dev(dict(x=x, w1_q=w1_q, w1_scale=w1_s, w2_q=w2_q, w2_scale=w2_s, topk_weight=tw, topk_ids=ti))
+    sh = dict(shared_w1=d["w1_q"][E - 1:].clone(), shared_w2=d["w2_q"][E - 1:].clone(),
+              shared_w1_scale=d["w1_scale"][E - 1:].clone(), shared_w2_scale=d["w2_scale"][E - 1:].clone())
+    for k in ("w1_q", "w2_q"):                         # the dummy row holds garbage until the call folds it in
+        d[k] = d[k].clone()
+        d[k].view(torch.uint8)[E - 1] = 0x7F
+    d["w1_scale"], d["w2_scale"] = d["w1_scale"].clone(), d["w2_scale"].clone()
+    d["w1_scale"][E - 1] = float("nan")
+    d["w2_scale"][E - 1] = float("nan")
+    out = run(d, shared_expert_id=E - 1, **sh)
+    assert_parity(out, ref, "separate shared expert weights")
+    with pytest.raises(ValueError, match="provided together"):
+        run(d, shared_w1=sh["shared_w1"])
+    with pytest.raises(ValueError, match="shared_expert_id == E - 1"):
+        run(d, shared_expert_id=0, **sh)
+
+
 def test_dsv3_decode_full_size(dsv3_layer):
     """cfg1: M=64, H=7168, I=2048, E=256, topk=8 with DeepSeek-V3 grouped routing; the oracle runs per expert on
     the host over the whole layer."""
