@@ -10,6 +10,8 @@ tuned-config dispatch and no fallback: options outside the FP8 1x128 / 128x128 p
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _lib
@@ -23,6 +25,7 @@ GEMM_BLOCK_M = 128         # row tile of the tcgen05 GEMM kernels == sort unit u
 quant_remap = {QuantType.per_128x128: QuantType.per_1x128}
 
 _status_words: dict[int, torch.Tensor] = {}
+_CHECK_STATUS_EVERY_CALL = os.environ.get("AITER_B200_CHECK_STATUS", "0") not in ("", "0")
 
 
 def _status(device: torch.device) -> torch.Tensor:
@@ -415,7 +418,13 @@ def fused_moe(
     in ``dtype`` (default: hidden_states.dtype; bf16 when that is fp8).
 
     ``block_size_M`` is accepted and ignored: the GEMM row tile is fixed at 128, which only
-    changes how the routes are padded, not the result."""
+    changes how the routes are padded, not the result.
+
+    The call only enqueues work. Should a device-side wait of a GEMM kernel ever run out (a broken pipeline; the
+    kernels then stop by themselves instead of hanging the GPU), the output is incomplete and a per-device status word
+    is set: call ``check_device_status()`` after synchronising to learn of it (it raises and clears the word). The word
+    is shared by all streams of a device. Setting ``AITER_B200_CHECK_STATUS=1`` makes every layer call check it (one
+    host synchronisation per call: a debugging aid, not for serving)."""
     quant_type = quant_remap.get(QuantType(quant_type), QuantType(quant_type))
     if quant_type not in (QuantType.per_1x128, QuantType.per_Token, QuantType.per_Tensor):
         raise NotImplementedError(
@@ -472,10 +481,13 @@ def fused_moe(
         _fold_shared_expert(w1, w2, w1_scale, w2_scale, shared, shared_expert_id, quant_type, expert_mask)
     if M == 0:   # nothing to compute: the reference allocates the same empty result (aiter/fused_moe.py:579-619)
         return torch.empty((0, model_dim), dtype=dtype, device=hidden_states.device)
-    return fused_moe_stages(hidden_states, w1.contiguous(), w2.contiguous(), topk_weight, topk_ids,
-                            expert_mask, w1_scale.contiguous(), w2_scale.contiguous(), a1_scale,
-                            num_local_tokens, dtype, quant_type=quant_type, activation=activation,
-                            doweight_stage1=bool(doweight_stage1))
+    out = fused_moe_stages(hidden_states, w1.contiguous(), w2.contiguous(), topk_weight, topk_ids,
+                           expert_mask, w1_scale.contiguous(), w2_scale.contiguous(), a1_scale,
+                           num_local_tokens, dtype, quant_type=quant_type, activation=activation,
+                           doweight_stage1=bool(doweight_stage1))
+    if _CHECK_STATUS_EVERY_CALL:
+        check_device_status(hidden_states.device)
+    return out
 
 
 # ------------------------------------------------------------------------------------- torch integration
