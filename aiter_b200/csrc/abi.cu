@@ -33,9 +33,6 @@ void launch_moe_stage2(const aiter_tensor_t*, const aiter_tensor_t*, const aiter
                        aiter_tensor_t*, aiter_tensor_t*, int, int, int, int, int, cudaStream_t);
 
 void set_gemm_debug(long long, int);
-#ifdef B200_ROLE_CLOCKS
-void set_role_clock_buffer(long long*);
-#endif
 
 void launch_biased_grouped_topk(const aiter_tensor_t*, const aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*, int, int,
                                 int, float, cudaStream_t);
@@ -205,13 +202,6 @@ B200_EXPORT int b200_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* 
 B200_EXPORT int b200_moe_debug_config(int64_t wait_limit_cycles, int stall_weight_producer) {
     return safe_call([&] { set_gemm_debug((long long)wait_limit_cycles, stall_weight_producer); });
 }
-
-#ifdef B200_ROLE_CLOCKS
-// Instrumented build only: device buffer (12 int64) that CTA 0 of the next GEMM launches fills with its per-role clock sums.
-B200_EXPORT int b200_moe_debug_role_clocks(int64_t device_ptr) {
-    return safe_call([&] { set_role_clock_buffer((long long*)(uintptr_t)device_ptr); });
-}
-#endif
 
 B200_EXPORT int b200_biased_grouped_topk(const aiter_tensor_t* gating_output, const aiter_tensor_t* correction_bias,
                                          aiter_tensor_t* topk_weights, aiter_tensor_t* topk_ids, int num_expert_group,

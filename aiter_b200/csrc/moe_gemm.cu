@@ -38,7 +38,8 @@ namespace {
 
 constexpr int BM = 128;            // sorted rows per tile (== sort unit)
 constexpr int BK = 128;            // K elements (bytes) per pipeline step == scale block
-constexpr int BN = 256;            // tile columns: 128 gate + 128 up, or 256 output columns
+constexpr int BN = 256;            // UMMA N: 128 gate + 128 up columns, or 256 output columns
+constexpr int kStages = 3;         // shared-memory pipeline depth (4 measured no faster; the space stages stage 2's output)
 constexpr int kABytes = BM * BK;   // 16 KB
 constexpr int kBBytes = BN * BK;   // 32 KB
 constexpr int kThreads = 512;
@@ -49,29 +50,21 @@ constexpr int kTmemCols = 512;     // 2 stages x 256 fp32 columns
 constexpr int kTmaSleepNs = 0;         // the single TMA thread polls without back-off
 constexpr int kProducerSleepNs = 100;  // back-off of the load roles while no stage is free
 constexpr int kEpilogueSleepNs = 40;   // back-off of the promotion warps while the UMMAs run
-constexpr int kScoutBar0 = 3;          // named barriers 3 and 4: scout warp <-> UMMA-issuing warp (1 and 2 are taken)
 constexpr uint32_t kIdesc = ptx::make_idesc_e4m3_f32(BM, BN);
-constexpr int kStageRowBytes = 272;   // staged output row of stage 2: 64 floats + 16 B (bank spread)
 
-// Shared memory map (offsets from a 1024-byte aligned base). The operand ring has 4 stages in stage 1 and 3 in
-// stage 2, whose staged output rows take the room of the fourth: a weight tile takes ~0.6-1.4k SM clocks to arrive
-// from L2 and longer from HBM, a K step ~0.6k, and a stage is free again only when its MMAs have completed.
-template <int STAGE>
-struct Smem {
-    static constexpr int kStages = STAGE == 1 ? 4 : 3;
-    static constexpr int kOffA = 0;
-    static constexpr int kOffB = kOffA + kStages * kABytes;
-    static constexpr int kOffBar = kOffB + kStages * kBBytes;          // mbarriers (8 B each)
-    static constexpr int kNumBars = 2 * kStages + 4;                   // full, empty per smem stage; tfull, tempty per TMEM stage
-    static constexpr int kOffTmemSlot = kOffBar + kNumBars * 8;
-    static constexpr int kOffAbort = kOffTmemSlot + 4;
-    static constexpr int kOffAmax = (kOffAbort + 4 + 15) & ~15;        // float [2 tiles][2 halves][128 rows]
-    static constexpr int kOffRowTab = kOffAmax + 2 * 2 * BM * 4;       // uint32 [2 tiles][128 rows]
-    static constexpr int kOffStage = (kOffRowTab + 2 * BM * 4 + 15) & ~15;   // [8 warps][32 rows][kStageRowBytes] (stage 2)
-    static constexpr int kUsed = kOffStage + (STAGE == 2 ? 8 * 32 * kStageRowBytes : 0);
-    static constexpr int kBytes = kUsed + 1024;                        // slack for the 1024-byte alignment
-    static_assert(kBytes <= 227 * 1024, "shared memory map exceeds the 227 KB a CTA may use");
-};
+// shared memory map (offsets from a 1024-byte aligned base)
+constexpr int kOffA = 0;
+constexpr int kOffB = kOffA + kStages * kABytes;
+constexpr int kOffBar = kOffB + kStages * kBBytes;          // mbarriers (8 B each)
+constexpr int kNumBars = 2 * kStages + 4;
+constexpr int kOffTmemSlot = kOffBar + kNumBars * 8;
+constexpr int kOffAbort = kOffTmemSlot + 4;
+constexpr int kOffAmax = (kOffAbort + 4 + 15) & ~15;        // float [2 tiles][2 halves][128 rows]
+constexpr int kOffRowTab = kOffAmax + 2 * 2 * BM * 4;       // uint32 [2 tiles][128 rows]
+constexpr int kStageRowBytes = 272;                            // staged output row: 64 floats + 16 B (bank spread)
+constexpr int kOffStage = (kOffRowTab + 2 * BM * 4 + 15) & ~15;   // [8 warps][32 rows][kStageRowBytes] (stage 2)
+constexpr int kSmemUsed = kOffStage + 8 * 32 * kStageRowBytes;
+constexpr int kSmemBytes = kSmemUsed + 1024;                // slack for the 1024-byte alignment
 
 struct GemmParams {
     const uint8_t* a;        // stage 1: a1 [M,K] by token; stage 2: a2 [P,K] by sorted row
@@ -95,26 +88,7 @@ struct GemmParams {
     int use_weight;          // multiply this stage's GEMM result by the route weight (sorted_w)
     long long wait_limit;    // SM clocks after which a device-side wait gives up (sets status, the CTA winds down)
     int stall_producer;      // self-test only: the weight producer loads nothing, so every wait downstream runs out
-#ifdef B200_ROLE_CLOCKS
-    long long* clocks;       // instrumented build: per-role SM-clock sums of CTA 0 (see RoleClock)
-#endif
 };
-
-// Instrumented build (-DB200_ROLE_CLOCKS): CTA 0 sums, per role, the SM clocks it spends in each wait and in its
-// work, and writes them to GemmParams::clocks. Compiled out otherwise.
-enum RoleClock { kClkTmaWait = 0, kClkGatherWait, kClkScoutTempty, kClkScoutFull, kClkMmaBarrier, kClkMmaIssue,
-                 kClkPromoWait, kClkPromoRead, kClkPromoTail, kClkEpilogue, kClkSteps, kClkTotal, kNumRoleClocks };
-#ifdef B200_ROLE_CLOCKS
-#define CLK_DECL(name) long long name = 0
-#define CLK_T(var) const long long var = clock64()
-#define CLK_ADD(acc, t0) acc += clock64() - (t0)
-#define CLK_OUT(slot, acc) do { if (blockIdx.x == 0 && p.clocks) p.clocks[slot] = (acc); } while (0)
-#else
-#define CLK_DECL(name)
-#define CLK_T(var)
-#define CLK_ADD(acc, t0)
-#define CLK_OUT(slot, acc)
-#endif
 
 // torch: silu(x) = x / (1 + exp(-x)) in fp32, then * up (aiter/fused_moe.py:3676).
 // The quotient is formed from an approximate reciprocal and one FMA residual correction (error below
@@ -179,20 +153,18 @@ __device__ __forceinline__ void fold16(float2* acc, const uint32_t* v, float2 s)
 template <int STAGE, bool PT, int ACT>
 __global__ void __launch_bounds__(kThreads, 1)
 moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) {
-    using L = Smem<STAGE>;
-    constexpr int kStages = L::kStages;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     const uint32_t sbase = ptx::smem_u32(smem);
-    const uint32_t sA = sbase + L::kOffA, sB = sbase + L::kOffB;
-    const uint32_t bar0 = sbase + L::kOffBar;
+    const uint32_t sA = sbase + kOffA, sB = sbase + kOffB;
+    const uint32_t bar0 = sbase + kOffBar;
     auto full_bar = [&](int s) { return bar0 + 8u * s; };
     auto empty_bar = [&](int s) { return bar0 + 8u * (kStages + s); };
-    auto tfull_bar = [&](int ts) { return bar0 + 8u * (2 * kStages + ts); };        // TMEM: two 256-column stages
-    auto tempty_bar = [&](int ts) { return bar0 + 8u * (2 * kStages + 2 + ts); };
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + L::kOffTmemSlot);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + L::kOffAbort);
-    float* amax_x = reinterpret_cast<float*>(smem + L::kOffAmax);
+    auto tfull_bar = [&](int s) { return bar0 + 8u * (2 * kStages + s); };
+    auto tempty_bar = [&](int s) { return bar0 + 8u * (2 * kStages + 2 + s); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + kOffTmemSlot);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(smem + kOffAbort);
+    float* amax_x = reinterpret_cast<float*>(smem + kOffAmax);
 
     const int warp = __shfl_sync(0xffffffffu, (int)(threadIdx.x >> 5), 0);
     const int lane = threadIdx.x & 31;
@@ -204,7 +176,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
         }
         for (int s = 0; s < 2; ++s) {
             ptx::mbar_init(tfull_bar(s), 1);                 // one tcgen05.commit
-            ptx::mbar_init(tempty_bar(s), kEpiThreads / 32); // one arrive per promotion warp
+            ptx::mbar_init(tempty_bar(s), kEpiThreads / 32); // one arrive per epilogue warp
         }
         *abort_flag = 0;
         ptx::fence_mbar_init();
@@ -224,132 +196,66 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
     const int total_tiles = (num_valid / BM) * p.n_tiles;
 
     if (warp < kGatherWarp0) {
-        ptx::setmaxnreg_dec<40>();
+        ptx::setmaxnreg_dec<24>();
         if (warp == 0 && lane == 0) {
             // ---------------------------------------------------------------- weight TMA producer
-            // Weight rows of the four 64-row boxes of a tile; column half h of the 256 tile columns holds box 2h then
-            // box 2h+1. Stage 1: [gate 64h.., up 64h..] of this 128-column n-tile, so that the promotion warps of half h
-            // own the gate and the up value of the same output columns in 128 adjacent TMEM columns; stage 2: 256
-            // consecutive output rows (the second half repeats the first where the n-tile is only half inside n_rows).
-            auto tile_rows = [&](int t, int (&rows)[4]) {
+            auto tile_rows = [&](int t, int& r0, int& r1) {
                 const int blk = t / p.n_tiles, nt = t - blk * p.n_tiles + p.nt0;
                 const int e = p.sorted_eids[blk];
                 if (STAGE == 1) {
-                    const int g0 = e * p.n_rows + nt * 128;
-                    rows[0] = g0; rows[1] = g0 + p.inter; rows[2] = g0 + 64; rows[3] = g0 + p.inter + 64;
+                    r0 = e * p.n_rows + nt * 128;   // gate rows
+                    r1 = r0 + p.inter;              // up rows
                 } else {
-                    const int r0 = e * p.n_rows + nt * 256;
-                    const bool whole = nt * 256 + 128 < p.n_rows;
-                    rows[0] = r0; rows[1] = r0 + 64; rows[2] = whole ? r0 + 128 : r0; rows[3] = whole ? r0 + 192 : r0 + 64;
+                    r0 = e * p.n_rows + nt * 256;
+                    r1 = (nt * 256 + 128 < p.n_rows) ? r0 + 128 : r0;
                 }
             };
             uint32_t it = 0;
             bool ok = !p.stall_producer;   // self-test: issue nothing; the other roles' waits then run out
-            CLK_DECL(c_wait);
             for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-                int rows[4];
-                tile_rows(t, rows);
+                int r0, r1;
+                tile_rows(t, r0, r1);
                 for (int kb = 0; kb < p.KB; ++kb, ++it) {
                     const int s = it % kStages;
                     const uint32_t ph = (it / kStages) & 1u;
-                    CLK_T(c0);
                     if (!(ok = ptx::mbar_wait<kTmaSleepNs>(empty_bar(s), ph ^ 1u, abort_flag, p.wait_limit))) break;
-                    CLK_ADD(c_wait, c0);
                     ptx::mbar_arrive_expect_tx(full_bar(s), kBBytes);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        ptx::tma_load_2d(sB + s * kBBytes + j * (kBBytes / 4), &tmap_w, kb * BK, rows[j], full_bar(s));
+                    ptx::tma_load_2d(sB + s * kBBytes, &tmap_w, kb * BK, r0, full_bar(s));
+                    ptx::tma_load_2d(sB + s * kBBytes + kBBytes / 2, &tmap_w, kb * BK, r1, full_bar(s));
                 }
             }
-            CLK_OUT(kClkTmaWait, c_wait);
-        } else if (warp == 1) {
+        } else if (warp == 1 && lane == 0) {
             // ---------------------------------------------------------------- UMMA issuer
             // Block scales (PT = false): every K block's partial sums go to the TMEM stage of that step's parity
             // and are promoted in registers. Row/channel scales (PT = true) do not depend on K: the whole K loop
             // accumulates in one TMEM stage, stages alternate per TILE, and the epilogue of a tile overlaps the
             // MMAs of the next.
-            // This warp executes NO mbarrier wait. Measured on B200: an mbarrier instruction that follows a burst of
-            // tcgen05.mma in program order completes only when those MMAs have been handed to the tensor core, which
-            // accepts them about one instruction ahead of execution; with the waits in this thread every K step
-            // opened a bubble of ~170 clocks per wait (620 instead of 512 clocks per step with one wait, 860 with two).
-            // The scout warp (warp 3) does the waiting and meets this warp at a hardware named barrier, which does
-            // not queue behind the MMAs; the commits stay here because they track this thread's MMAs.
-            // flat loop over this CTA's K steps with incrementally kept ring positions (this role runs on 40 registers)
-            const int my_tiles = ((int)blockIdx.x < total_tiles) ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-            const uint32_t n_steps = (uint32_t)my_tiles * (uint32_t)p.KB;
-            uint32_t stage = 0, ts = 0;
-            int kb = 0;
-            CLK_DECL(c_bar);
-            CLK_DECL(c_issue);
-            CLK_T(c_begin);
-            for (uint32_t it = 0; it < n_steps; ++it) {
-                CLK_T(c0);
-                ptx::named_barrier(kScoutBar0 + (it & 1u), 64);   // the scout saw this step's operands and TMEM stage
-                CLK_ADD(c_bar, c0);
-                const bool last_kb = kb == p.KB - 1;
-                if (!*abort_flag) {                                // after a give-up: keep meeting the scout, issue nothing
-                    CLK_T(c1);
-                    if (lane == 0) {
-                        ptx::tc_fence_after();
-                        const uint64_t da = ptx::make_kmajor_sw128_desc(sA + stage * kABytes);
-                        const uint64_t db = ptx::make_kmajor_sw128_desc(sB + stage * kBBytes);
-                        const uint32_t d = tmem_base + ts * BN;
-#pragma unroll
-                        for (int k = 0; k < BK / 32; ++k)   // 32 bytes of K per UMMA: +2 in 16-byte units
-                            ptx::umma_f8(d, da + 2u * k, db + 2u * k, kIdesc, (k > 0 || (PT && kb > 0)) ? 1u : 0u);
-                        ptx::umma_commit(empty_bar(stage));
-                        if (!PT || last_kb) ptx::umma_commit(tfull_bar(ts));
-                    }
-                    __syncwarp();
-                    CLK_ADD(c_issue, c1);
-                }
-                stage = (stage + 1 == (uint32_t)kStages) ? 0 : stage + 1;
-                if (!PT || last_kb) ts ^= 1u;                      // PT: the TMEM stage changes per tile, else per K step
-                kb = last_kb ? 0 : kb + 1;
-            }
-#ifdef B200_ROLE_CLOCKS
-            if (lane == 0) {
-                CLK_OUT(kClkMmaBarrier, c_bar);
-                CLK_OUT(kClkMmaIssue, c_issue);
-                CLK_OUT(kClkSteps, (long long)n_steps);
-                CLK_OUT(kClkTotal, clock64() - c_begin);
-            }
-#endif
-        } else if (warp == 3) {
-            // ---------------------------------------------------------------- scout: waits on behalf of the UMMA issuer
-            const int my_tiles = ((int)blockIdx.x < total_tiles) ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-            const uint32_t n_steps = (uint32_t)my_tiles * (uint32_t)p.KB;
-            uint32_t stage = 0, ph = 0, ts = 0, tph = 0;   // smem ring position / parity, TMEM ring position / parity
-            int kb = 0;
+            uint32_t it = 0, tile_it = 0;
             bool ok = true;
-            CLK_DECL(c_te);
-            CLK_DECL(c_fu);
-            for (uint32_t it = 0; it < n_steps; ++it) {
-                const bool last_kb = kb == p.KB - 1;
-                if (ok && lane == 0) {
-                    CLK_T(c0);
-                    if (!PT || kb == 0) ok = ptx::mbar_wait(tempty_bar(ts), tph ^ 1u, abort_flag, p.wait_limit);
-                    CLK_ADD(c_te, c0);
-                    CLK_T(c1);
-                    if (ok) ok = ptx::mbar_wait(full_bar(stage), ph, abort_flag, p.wait_limit);
-                    CLK_ADD(c_fu, c1);
+            for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++tile_it) {
+                for (int kb = 0; kb < p.KB; ++kb, ++it) {
+                    const int s = it % kStages;
+                    const uint32_t ph = (it / kStages) & 1u;
+                    const uint32_t tcount = PT ? tile_it : it;   // what the TMEM stage ring counts
+                    const int ts = tcount & 1;
+                    const uint32_t tph = (tcount >> 1) & 1u;
+                    if (!PT || kb == 0)
+                        if (!(ok = ptx::mbar_wait(tempty_bar(ts), tph ^ 1u, abort_flag, p.wait_limit))) break;
+                    if (!(ok = ptx::mbar_wait(full_bar(s), ph, abort_flag, p.wait_limit))) break;
                     // the activation rows were written by cp.async (generic proxy); order them
                     // before the tensor core's async-proxy reads
                     ptx::fence_proxy_async();
+                    ptx::tc_fence_after();
+                    const uint64_t da = ptx::make_kmajor_sw128_desc(sA + s * kABytes);
+                    const uint64_t db = ptx::make_kmajor_sw128_desc(sB + s * kBBytes);
+                    const uint32_t d = tmem_base + ts * BN;
+#pragma unroll
+                    for (int k = 0; k < BK / 32; ++k)   // 32 bytes of K per UMMA: +2 in 16-byte units
+                        ptx::umma_f8(d, da + 2u * k, db + 2u * k, kIdesc, (k > 0 || (PT && kb > 0)) ? 1u : 0u);
+                    ptx::umma_commit(empty_bar(s));
+                    if (!PT || kb == p.KB - 1) ptx::umma_commit(tfull_bar(ts));
                 }
-                ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-                // after a give-up the scout keeps arriving (without waiting) so that the issuer never blocks here
-                ptx::named_barrier(kScoutBar0 + (it & 1u), 64);
-                if (stage + 1 == (uint32_t)kStages) { stage = 0; ph ^= 1u; } else ++stage;
-                if (!PT || last_kb) { tph ^= ts; ts ^= 1u; }       // parity flips each time the ring wraps to stage 0
-                kb = last_kb ? 0 : kb + 1;
             }
-#ifdef B200_ROLE_CLOCKS
-            if (lane == 0) {
-                CLK_OUT(kClkScoutTempty, c_te);
-                CLK_OUT(kClkScoutFull, c_fu);
-            }
-#endif
         }
     } else if (warp < kEpiWarp0) {
         // -------------------------------------------------------------------- activation gather
@@ -360,11 +266,10 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
         // thread covers row gw*32 + i*4 + lane/8.
         const int gw = r >> 5, sub = (r & 31) >> 3;
         const uint32_t chunk = (uint32_t)(r & 7);
-        uint32_t* row_tab = reinterpret_cast<uint32_t*>(smem + L::kOffRowTab);   // [2][128] source rows
+        uint32_t* row_tab = reinterpret_cast<uint32_t*>(smem + kOffRowTab);   // [2][128] source rows
         uint32_t it = 0;
         uint32_t tile_par = 0;
         bool ok = true;
-        CLK_DECL(c_gwait);
         int sid_next = 0;   // sorted id of this thread's row in the next tile, fetched one tile ahead
         if (STAGE == 1 && (int)blockIdx.x < total_tiles)
             sid_next = p.sorted_ids[((int)blockIdx.x / p.n_tiles) * BM + r];
@@ -399,9 +304,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
             for (int kb = 0; kb < p.KB; ++kb, ++it) {
                 const int s = it % kStages;
                 const uint32_t ph = (it / kStages) & 1u;
-                CLK_T(c0);
                 if (!(ok = ptx::mbar_wait<kProducerSleepNs>(empty_bar(s), ph ^ 1u, abort_flag, p.wait_limit))) break;
-                CLK_ADD(c_gwait, c0);
                 const uint32_t dst = sA + s * kABytes;
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
@@ -414,22 +317,16 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
         }
         ptx::cp_async_commit();
         ptx::cp_async_wait<0>();   // nothing of this thread is in flight when the CTA winds down
-#ifdef B200_ROLE_CLOCKS
-        if (r == 0) CLK_OUT(kClkGatherWait, c_gwait);
-#endif
     } else {
         // -------------------------------------------------------------------- promotion + epilogue
-        ptx::setmaxnreg_inc<208>();
+        ptx::setmaxnreg_inc<216>();
         const int q = warp & 3;                         // TMEM lane quarter this warp may read
-        const int half = (warp - kEpiWarp0) >> 2;       // column half of the tile this warp promotes: TMEM columns [128*half, 128*half + 128)
+        const int half = (warp - kEpiWarp0) >> 2;       // which 64 columns of each 128-column group
         const int r = q * 32 + lane;                    // row of the tile == TMEM lane
         const uint32_t lane_addr = tmem_base + ((uint32_t)(q * 32) << 16);
         uint32_t it = 0;
         uint32_t tile_par = 0;
         bool ok = true;
-#ifdef B200_ROLE_CLOCKS
-        unsigned c_pwait = 0, c_pread = 0, c_pepi = 0;   // 32-bit sums: this role has no registers to spare
-#endif
         // row info of the next tile is fetched one tile ahead, so its latency is off the path between
         // two tiles (where the MMA warp can only run two K steps ahead of these warps)
         int tok_next = 0, eid_next = 0;
@@ -469,9 +366,8 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
             const uint32_t a_so = (uint32_t)(valid ? (STAGE == 1 ? tok : prow) : 0) * (uint32_t)(PT ? 1 : p.KB);
             uint32_t w_so = 0, w_so1 = 0;
             if (!PT) {
-                // stage 1: gate block nt and up block I/128 + nt; stage 2: this half's one 128-column block
-                const int nb0 = (STAGE == 1) ? nt : min(nt * 2 + half, p.n_rows / 128 - 1);
-                const int nb1 = (STAGE == 1) ? p.inter / 128 + nt : nb0;
+                const int nb0 = (STAGE == 1) ? nt : nt * 2;
+                const int nb1 = (STAGE == 1) ? p.inter / 128 + nt : min(nt * 2 + 1, p.n_rows / 128 - 1);
                 w_so = (uint32_t)((eid * (p.n_rows / 128) + nb0) * p.KB);
                 w_so1 = w_so + (uint32_t)((nb1 - nb0) * p.KB);
             }
@@ -481,14 +377,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
             for (int kb = PT ? p.KB - 1 : 0; kb < p.KB; ++kb, ++it) {
                 const int ts = it & 1;
                 const uint32_t tph = (it >> 1) & 1u;
-#ifdef B200_ROLE_CLOCKS
-                const unsigned c0 = (unsigned)clock64();
-#endif
                 if (!(ok = ptx::mbar_wait<kEpilogueSleepNs>(tfull_bar(ts), tph, abort_flag, p.wait_limit))) break;
-#ifdef B200_ROLE_CLOCKS
-                const unsigned c1 = (unsigned)clock64();
-                c_pwait += c1 - c0;
-#endif
                 ptx::tc_fence_after();
                 const float sa = pf_a * wgt;   // wgt is exactly 1 when the stage does not weight
                 const float s0 = PT ? sa : sa * pf_w0, s1 = PT ? sa : sa * pf_w1;
@@ -498,7 +387,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                     pf_w1 = __ldg(p.w_scale + w_so1 + kb + 1);
                 }
                 const float2 s0v = make_float2(s0, s0), s1v = make_float2(s1, s1);
-                const uint32_t ta = lane_addr + ts * BN + half * 128;   // 64 first-group then 64 second-group columns
+                const uint32_t ta = lane_addr + ts * BN + half * 64;
                 // load + wait, then packed FMAs.  The packed fp32x2 FMAs matter:
                 // they need half the issue slots of scalar FMAs, and with scalar FMAs the two promotion
                 // warps that share a scheduler with the UMMA-issuing warp starve it (measured: the UMMA
@@ -509,31 +398,25 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                 if (warp_live) {
 #pragma unroll
                     for (int c = 0; c < 7; ++c) {
-                        ptx::tmem_ld_x16_sync(ta + c * 16, v);
+                        ptx::tmem_ld_x16_sync(ta + (c >> 2) * 128 + (c & 3) * 16, v);
                         fold16(acc + 8 * c, v, (c < 4) ? s0v : s1v);
                     }
-                    ptx::tmem_ld_x16_sync(ta + 7 * 16, v);
+                    ptx::tmem_ld_x16_sync(ta + 128 + 48, v);
                 }
                 // all reads of this TMEM stage are done: hand it back to the MMA warp
                 ptx::tc_fence_before();
                 __syncwarp();
                 if (lane == 0) ptx::mbar_arrive(tempty_bar(ts));
-#ifdef B200_ROLE_CLOCKS
-                c_pread += (unsigned)clock64() - c1;
-#endif
                 if (warp_live) fold16(acc + 56, v, s1v);
             }
             if (!ok) break;
-#ifdef B200_ROLE_CLOCKS
-            const unsigned c2 = (unsigned)clock64();
-#endif
 
             if (PT) {
                 // weight scales per output channel: column j of the first group is weight row
                 // e*n_rows + c0 + j, of the second group c1 + j (all lanes read the same addresses)
                 const int e = p.sorted_eids[blk];
-                const int c0 = (STAGE == 1) ? nt * 128 + half * 64 : min(nt * 256 + half * 128, p.n_rows - 128);
-                const int c1 = (STAGE == 1) ? p.inter + c0 : c0 + 64;
+                const int c0 = (STAGE == 1) ? nt * 128 + half * 64 : nt * 256 + half * 64;
+                const int c1 = (STAGE == 1) ? p.inter + c0 : min(c0 + 128, p.n_rows - 64);
                 const float4* w0 = reinterpret_cast<const float4*>(p.w_scale + (size_t)e * p.n_rows + c0);
                 const float4* w1 = reinterpret_cast<const float4*>(p.w_scale + (size_t)e * p.n_rows + c1);
 #pragma unroll
@@ -630,38 +513,27 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
                 // red.global.v4 from registers or as bulk reductions (plain stores: ~35 B/clock), i.e. ~6k clocks
                 // per tile that the MMA warp, at most two K steps ahead, waits out; hiding them needs a buffer
                 // for the whole 128 KB tile, which neither shared nor tensor memory has room for.
-                const uint32_t srow = sbase + L::kOffStage + (uint32_t)((warp - kEpiWarp0) * 32 + lane) * kStageRowBytes;
-                // the second half of the last n-tile lies outside n_rows when n_rows % 256 == 128
-                const bool half_live = nt * 256 + half * 128 < p.n_rows;
-                if (valid && half_live) {
-                    float* orow = p.acc + (size_t)tok * p.acc_ld + (nt - p.nt0) * 256 + half * 128;
+                const uint32_t srow = sbase + kOffStage + (uint32_t)((warp - kEpiWarp0) * 32 + lane) * kStageRowBytes;
+                const int n_groups = (nt * 256 + 128 < p.n_rows) ? 2 : 1;
+                if (valid) {
+                    float* orow = p.acc + (size_t)tok * p.acc_ld + (nt - p.nt0) * 256 + half * 64;
 #pragma unroll
                     for (int g = 0; g < 2; ++g) {
-                        {
+                        if (g < n_groups) {
                             ptx::bulk_wait_read_all();   // the copy engine has read this row's previous contents
 #pragma unroll
                             for (int j = 0; j < 16; ++j)
                                 ptx::st_shared_v4(srow + j * 16, acc[g * 32 + 2 * j].x, acc[g * 32 + 2 * j].y,
                                                   acc[g * 32 + 2 * j + 1].x, acc[g * 32 + 2 * j + 1].y);
                             ptx::fence_proxy_async();
-                            ptx::bulk_reduce_add_f32(orow + g * 64, srow, 256);
+                            ptx::bulk_reduce_add_f32(orow + g * 128, srow, 256);
                             ptx::bulk_commit();
                         }
                     }
                 }
             }
-#ifdef B200_ROLE_CLOCKS
-            c_pepi += (unsigned)clock64() - c2;
-#endif
         }
         ptx::bulk_wait_all();   // nothing of this thread is in flight when the CTA winds down
-#ifdef B200_ROLE_CLOCKS
-        if (warp == kEpiWarp0 && lane == 0) {
-            CLK_OUT(kClkPromoWait, (long long)c_pwait);
-            CLK_OUT(kClkPromoRead, (long long)c_pread);
-            CLK_OUT(kClkEpilogue, (long long)c_pepi);
-        }
-#endif
     }
 
     // ------------------------------------------------------------------------ tail
@@ -700,17 +572,32 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// 2-D view [rows, K] of an fp8 weight tensor [E, n_rows, K]; boxes of 64 rows x 128 bytes, 128B swizzle.
+// 2-D view [rows, K] of an fp8 weight tensor [E, n_rows, K]; boxes of 128 rows x 128 bytes, 128B swizzle. Encoding a map
+// costs a few microseconds of host time, so the last maps are kept (per thread) and reused while pointer and shape
+// repeat, as they do from layer call to layer call.
 CUtensorMap make_weight_map(const void* ptr, uint64_t rows, uint64_t K) {
+    struct Entry {
+        const void* ptr;
+        uint64_t rows, K;
+        CUtensorMap map;
+    };
+    constexpr int kEntries = 16;
+    static thread_local Entry cache[kEntries];
+    static thread_local int next = 0, used = 0;
+    for (int i = 0; i < used; ++i)
+        if (cache[i].ptr == ptr && cache[i].rows == rows && cache[i].K == K) return cache[i].map;
     CUtensorMap m;
     cuuint64_t dims[2] = {K, rows};
     cuuint64_t strides[1] = {K};
-    cuuint32_t box[2] = {128, 64};
+    cuuint32_t box[2] = {128, 128};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = encode_tiled_fn()(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides,
                                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     B200_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", (int)r);
+    cache[next] = Entry{ptr, rows, K, m};
+    next = (next + 1) % kEntries;
+    if (used < kEntries) ++used;
     return m;
 }
 
@@ -718,9 +605,6 @@ CUtensorMap make_weight_map(const void* ptr, uint64_t rows, uint64_t K) {
 // clocks, and whether the weight producer is stalled. Defaults: the built-in limit, no stall.
 long long g_wait_limit = ptx::kWaitLimitCycles;
 int g_stall_producer = 0;
-#ifdef B200_ROLE_CLOCKS
-long long* g_role_clocks = nullptr;   // device buffer of kNumRoleClocks values, set by b200_moe_debug_role_clocks
-#endif
 
 template <int STAGE, bool PT, int ACT = 0>
 void launch_gemm(const CUtensorMap& tmap, const GemmParams& p, int64_t max_tiles, int dev, cudaStream_t stream,
@@ -728,7 +612,7 @@ void launch_gemm(const CUtensorMap& tmap, const GemmParams& p, int64_t max_tiles
     static bool attr_set[64] = {false};
     if (dev >= 64 || !attr_set[dev]) {
         B200_CUDA(cudaFuncSetAttribute(moe_gemm_kernel<STAGE, PT, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       Smem<STAGE>::kBytes));
+                                       kSmemBytes));
         if (dev < 64) attr_set[dev] = true;
     }
     B200_CHECK(sm_margin < sm_count(dev), "sm_margin (", sm_margin, ") must leave at least one of the device's ",
@@ -739,18 +623,11 @@ void launch_gemm(const CUtensorMap& tmap, const GemmParams& p, int64_t max_tiles
     GemmParams q = p;
     q.wait_limit = g_wait_limit;
     q.stall_producer = g_stall_producer;
-#ifdef B200_ROLE_CLOCKS
-    q.clocks = g_role_clocks;
-#endif
-    moe_gemm_kernel<STAGE, PT, ACT><<<(unsigned)grid, kThreads, Smem<STAGE>::kBytes, stream>>>(tmap, q);
+    moe_gemm_kernel<STAGE, PT, ACT><<<(unsigned)grid, kThreads, kSmemBytes, stream>>>(tmap, q);
     B200_CUDA(cudaGetLastError());
 }
 
 }  // namespace
-
-#ifdef B200_ROLE_CLOCKS
-void set_role_clock_buffer(long long* dev_ptr) { g_role_clocks = dev_ptr; }
-#endif
 
 void set_gemm_debug(long long wait_limit_cycles, int stall_producer) {
     g_wait_limit = wait_limit_cycles > 0 ? wait_limit_cycles : ptx::kWaitLimitCycles;

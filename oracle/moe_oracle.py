@@ -263,7 +263,9 @@ def error_stats(out: torch.Tensor, ref: torch.Tensor, atol=1e-2, rtol=1e-2):
     max_abs_excl_one_ulp_over_rms: the first figure over the elements that are NOT exact one-ulp
     neighbours of the reference. One bf16 ulp of an element above ~2.6 RMS is already more than
     2 % of RMS, so at millions of outputs a single flipped final rounding on a large element
-    decides the strict figure; this one shows what is left beside such flips."""
+    decides the strict figure; this one shows what is left beside such flips.
+    n_two_steps: elements two representable bf16 values away from the reference; max_bf16_steps: the largest such
+    distance over same-sign pairs (large for values next to zero, where it means nothing)."""
     o = out.detach().to("cpu", torch.float32)
     r = ref.detach().to("cpu", torch.float32)
     d = (o - r).abs()
@@ -271,15 +273,21 @@ def error_stats(out: torch.Tensor, ref: torch.Tensor, atol=1e-2, rtol=1e-2):
     within = float((d <= atol + rtol * r.abs()).float().mean())
     n_diff = int((d > 0).sum())
     n_one_ulp = 0
+    n_two_steps = 0
+    max_steps = None
     max_excl = float(d.max())
     if out.dtype == torch.bfloat16 and ref.dtype == torch.bfloat16:
         ob = out.detach().cpu().view(torch.int16).to(torch.int32)
         rb = ref.detach().cpu().view(torch.int16).to(torch.int32)
-        one = (ob - rb).abs() == 1          # neighbouring bf16 values (same sign): one final rounding flipped
+        steps = (ob - rb).abs()             # distance in representable bf16 values (same sign)
+        one = steps == 1                    # neighbouring bf16 values: one final rounding flipped
         n_one_ulp = int(one.sum())
+        n_two_steps = int((steps == 2).sum())
+        same_sign = (ob ^ rb) >= 0
+        max_steps = int(steps[same_sign].max()) if bool(same_sign.any()) else 0
         max_excl = float(d.masked_fill(one, 0.0).max())
     return dict(max_abs=float(d.max()), rms=rms,
                 max_abs_over_rms=float(d.max()) / max(rms, 1e-30),
                 max_abs_excl_one_ulp_over_rms=max_excl / max(rms, 1e-30),
-                frac_within=within, n_diff=n_diff, n_one_ulp=n_one_ulp,
-                numel=o.numel(), has_nan=bool(torch.isnan(o).any()))
+                frac_within=within, n_diff=n_diff, n_one_ulp=n_one_ulp, n_two_steps=n_two_steps,
+                max_bf16_steps=max_steps, numel=o.numel(), has_nan=bool(torch.isnan(o).any()))

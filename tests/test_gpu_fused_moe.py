@@ -36,7 +36,7 @@ def run(c, **kw):
     return out
 
 
-def assert_parity(out, ref, tag, strict=False):
+def assert_parity(out, ref, tag, strict=False, whole_layer=False):
     """strict: max |d| <= 2 % of RMS over all elements. A single flipped final bf16 rounding on an
     element above ~2.6 RMS exceeds that by itself (its ulp is larger than 2 % of RMS), and the fp32
     reductions of stage 2 land in a different order on every run, so which roundings flip changes
@@ -52,6 +52,13 @@ def assert_parity(out, ref, tag, strict=False):
     assert s["frac_within"] >= FRAC_WITHIN, (tag, s)
     if strict:
         assert s["max_abs_over_rms"] <= MAX_ABS_OVER_RMS, (tag, s)
+    elif whole_layer:
+        # 10^7..10^8 outputs: beside the one-step flips some elements (0.2 %) sit TWO representable bf16 values from
+        # the reference, and two steps across the binade boundary at 2.0 (0.0117) are already 2.2 % of an RMS of 0.53.
+        # Asserted: every element within atol = rtol = 1e-2, and the magnitude bounds that two bf16 steps imply.
+        assert s["frac_within"] == 1.0, (tag, s)
+        assert s["max_abs_excl_one_ulp_over_rms"] <= 1.5 * MAX_ABS_OVER_RMS, (tag, s)
+        assert s["max_abs_over_rms"] <= 2 * MAX_ABS_OVER_RMS, (tag, s)
     else:
         assert s["max_abs_excl_one_ulp_over_rms"] <= MAX_ABS_OVER_RMS, (tag, s)
         assert s["max_abs_over_rms"] <= 2 * MAX_ABS_OVER_RMS, (tag, s)
@@ -265,7 +272,7 @@ def test_dsv3_prefill_whole_layer(dsv3_layer):
     torch.set_num_threads(len(os.sched_getaffinity(0)))
     ref = moe_oracle.fused_moe_ref(c["x"].cpu(), cpu["w1_q"], cpu["w1_scale"], cpu["w2_q"], cpu["w2_scale"],
                                    c["topk_weight"].cpu(), c["topk_ids"].cpu())
-    assert_parity(out, ref, "cfg2 prefill M=8192 (whole layer)", strict=False)
+    assert_parity(out, ref, "cfg2 prefill M=8192 (whole layer)", whole_layer=True)
     del ref
     c2 = dict(c)
     c2["topk_weight"] = c["topk_weight"] * 2
