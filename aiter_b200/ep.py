@@ -114,6 +114,10 @@ class PeerExchange:
     must reach it)."""
 
     _cache: dict = {}
+    # (device index, 64-byte IPC handle) -> mapped base address. torch's allocator carves several tensors out of one
+    # cudaMalloc segment; two arenas in one segment export the SAME handle (with different offsets), and a process may
+    # open a handle only once, so mappings are shared between exchanges and closed together in clear().
+    _opened: dict = {}
 
     def __init__(self, group, m_local, H, device):
         import ctypes
@@ -150,11 +154,13 @@ class PeerExchange:
                     if r == rank:
                         bases.append(self.arena.data_ptr())
                         continue
-                    base = ctypes.c_int64(0)
-                    _lib.call_plain("b200_ep_ipc_open", ctypes.create_string_buffer(exported[r][0], 64),
-                                    int(device.index), ctypes.byref(base))
-                    self.mapped.append(int(base.value))
-                    bases.append(int(base.value) + exported[r][1])
+                    key = (int(device.index), bytes(exported[r][0]))
+                    if key not in PeerExchange._opened:
+                        base = ctypes.c_int64(0)
+                        _lib.call_plain("b200_ep_ipc_open", ctypes.create_string_buffer(exported[r][0], 64),
+                                        int(device.index), ctypes.byref(base))
+                        PeerExchange._opened[key] = int(base.value)
+                    bases.append(PeerExchange._opened[key] + exported[r][1])
             except RuntimeError as e:
                 err = str(e)
         else:
@@ -168,8 +174,7 @@ class PeerExchange:
         self.ptrs_recv, self.ptrs_a1, self.ptrs_a1_scale = table(off_recv), table(off_a1), table(off_a1s)
 
     def close(self):
-        for base in self.mapped:
-            _lib.call_plain("b200_ep_ipc_close", base, int(self.device.index))
+        """Mappings are shared between exchanges (see ``_opened``) and are closed by ``clear()``."""
         self.mapped = []
 
     @classmethod
@@ -188,6 +193,9 @@ class PeerExchange:
         for ex in cls._cache.values():
             ex.close()
         cls._cache.clear()
+        for (dev_index, _handle), base in cls._opened.items():
+            _lib.call_plain("b200_ep_ipc_close", base, dev_index)
+        cls._opened.clear()
 
 
 def _p2p_combine(ex, partial, ids, num_experts, group, dtype, timers, expert_rank=None):

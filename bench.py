@@ -131,20 +131,22 @@ def make_layer(device, rank, world, seed=0):
     return w1_q, w1_s, w2_q, w2_s
 
 
-def router_inputs(M, seed=0):
-    """Seeded activations, router logits ~ N(0,1) and correction bias ~ N(0, 0.1) (host generator)."""
+def router_inputs(M, seed=0, bias=None):
+    """Seeded activations, router logits ~ N(0,1) and correction bias ~ N(0, 0.1) (host generator). ``bias``: reuse
+    the correction bias of another batch (it is a model parameter: a calibration batch for the expert placement has
+    the model's bias, not one of its own)."""
     g = torch.Generator().manual_seed(seed)
     x = torch.randn((M, H), generator=g, dtype=torch.float32).to(torch.bfloat16)
     g = torch.Generator().manual_seed(seed + 3)
     logits = torch.randn((M, E), generator=g, dtype=torch.float32)
-    bias = torch.randn((E,), generator=g, dtype=torch.float32) * 0.1
-    return x, logits, bias
+    own_bias = torch.randn((E,), generator=g, dtype=torch.float32) * 0.1
+    return x, logits, own_bias if bias is None else bias
 
 
-def make_tokens(M, seed=0, device=None):
+def make_tokens(M, seed=0, device=None, bias=None):
     """x [M,H] bf16 and DeepSeek-V3 routing (8 groups, top-4 groups, top-8 experts, renormalised, x2.5): computed by
     this library's own router kernel on `device`; on the host (the CPU legs, device=None) by the oracle's router."""
-    x, logits, bias = router_inputs(M, seed)
+    x, logits, bias = router_inputs(M, seed, bias)
     if device is None:
         from oracle import moe_oracle
         tw, ti = moe_oracle.biased_grouped_topk_ref(logits, bias, TOPK, True, 8, 4, routed_scaling_factor=2.5)
@@ -408,8 +410,10 @@ def bench_other_configs(dev, rank, world, sync, max_over_ranks, exchange, steps)
 
 
 def ep_parity_check(out_local, x, tw, ti, w, table, rank, world, dev, n_rows=4):
-    """N > 1: the first rows of rank 0's output against the CPU oracle. The experts those rows are routed to are
-    fetched from the ranks that own them (broadcasts, outside every timed region); the oracle then runs on rank 0."""
+    """N > 1: the first rows of rank 0's output against the CPU oracle. ``x``, ``tw``, ``ti`` are RANK 0's rows on every
+    rank (all ranks must walk the same expert list); ``out_local`` is the caller's own output and is read on rank 0
+    only. The experts those rows are routed to are fetched from the ranks that own them (broadcasts, outside every
+    timed region); the oracle then runs on rank 0."""
     import torch.distributed as dist
     w1_q, w1_s, w2_q, w2_s = w
     rows_ids = ti[:n_rows]
@@ -496,7 +500,9 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        # a collective that not every rank reaches ends with an error after this time instead of hanging the job
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
 
     def sync():
         torch.cuda.synchronize()
@@ -525,7 +531,7 @@ def main():
     table = torch.arange(E, dtype=torch.int32) // (E // world)
     placement_info = None
     if world > 1 and args.ep_placement == "balanced":
-        _xc, _twc, tic = make_tokens(M_PREFILL, seed=100, device=dev)
+        _xc, _twc, tic = make_tokens(M_PREFILL, seed=100, device=dev, bias=router_inputs(M_PREFILL)[2])
         table = ep.balanced_expert_placement(torch.bincount(tic.flatten().long(), minlength=E), world)
     if world > 1:
         counts = torch.bincount(ti.flatten().long(), minlength=E)
@@ -660,8 +666,9 @@ def main():
         # numerical check of the path that was just timed (outside the timed region)
         out_chk = step_dev()
         torch.cuda.synchronize()
-        line["parity_check"] = ep_parity_check(out_chk, x[rows], tw[rows], ti[rows], (w1_q, w1_s, w2_q, w2_s), table, rank,
-                                               world, dev)
+        # every rank walks the SAME list of experts (those of rank 0's first rows), each broadcast by its owner
+        line["parity_check"] = ep_parity_check(out_chk, x[:m_local], tw[:m_local], ti[:m_local], (w1_q, w1_s, w2_q, w2_s),
+                                               table, rank, world, dev)
 
     if not args.skip_decode and not small and M_DECODE % world == 0:
         # ---- decode case (M=64): HBM-bound weight streaming; N > 1: the same expert-parallel path, 64/N rows per rank
