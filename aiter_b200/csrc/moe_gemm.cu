@@ -47,9 +47,21 @@ constexpr int kGatherWarp0 = 4;    // warps 4..7
 constexpr int kEpiWarp0 = 8;       // warps 8..15
 constexpr int kEpiThreads = 256;
 constexpr int kTmemCols = 512;     // 2 stages x 256 fp32 columns
+// Registers per thread of each role after setmaxnreg. A CTA's pool is what the launch gave it (registers per thread
+// of the compiled kernel x threads); setmaxnreg.inc BLOCKS until the pool covers the request, for ever if the other
+// roles never release enough, so the sum is checked at compile time against the launch bound and again at the
+// first launch against what the compiler really assigned.
+constexpr int kRegsLoad = 24, kRegsGather = 56, kRegsPromo = 216;
+constexpr int kRegDemand = 32 * (kGatherWarp0 * kRegsLoad + (kEpiWarp0 - kGatherWarp0) * kRegsGather +
+                                 (kThreads / 32 - kEpiWarp0) * kRegsPromo);
+static_assert(kRegDemand <= 65536 && kRegDemand <= kThreads * (65536 / kThreads),
+              "setmaxnreg: the roles ask for more registers than the CTA is launched with");
 constexpr int kTmaSleepNs = 0;         // the single TMA thread polls without back-off
 constexpr int kProducerSleepNs = 100;  // back-off of the load roles while no stage is free
-constexpr int kEpilogueSleepNs = 40;   // back-off of the promotion warps while the UMMAs run
+#ifndef B200_EPI_SLEEP_NS
+#define B200_EPI_SLEEP_NS 40
+#endif
+constexpr int kEpilogueSleepNs = B200_EPI_SLEEP_NS;   // back-off of the promotion warps while the UMMAs run
 constexpr uint32_t kIdesc = ptx::make_idesc_e4m3_f32(BM, BN);
 
 // shared memory map (offsets from a 1024-byte aligned base)
@@ -196,7 +208,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
     const int total_tiles = (num_valid / BM) * p.n_tiles;
 
     if (warp < kGatherWarp0) {
-        ptx::setmaxnreg_dec<24>();
+        ptx::setmaxnreg_dec<kRegsLoad>();
         if (warp == 0 && lane == 0) {
             // ---------------------------------------------------------------- weight TMA producer
             auto tile_rows = [&](int t, int& r0, int& r1) {
@@ -259,7 +271,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
         }
     } else if (warp < kEpiWarp0) {
         // -------------------------------------------------------------------- activation gather
-        ptx::setmaxnreg_dec<56>();
+        ptx::setmaxnreg_dec<kRegsGather>();
         const int r = threadIdx.x - kGatherWarp0 * 32;   // row whose scale / row offset this thread owns
         // Copy mapping: 8 consecutive lanes fetch the eight 16-byte chunks of one 128-byte row segment,
         // so a warp-wide cp.async touches 4 whole cache lines (not 32 partial ones). Pass i of a
@@ -319,7 +331,7 @@ moe_gemm_kernel(const __grid_constant__ CUtensorMap tmap_w, const GemmParams p) 
         ptx::cp_async_wait<0>();   // nothing of this thread is in flight when the CTA winds down
     } else {
         // -------------------------------------------------------------------- promotion + epilogue
-        ptx::setmaxnreg_inc<216>();
+        ptx::setmaxnreg_inc<kRegsPromo>();
         const int q = warp & 3;                         // TMEM lane quarter this warp may read
         const int half = (warp - kEpiWarp0) >> 2;       // which 64 columns of each 128-column group
         const int r = q * 32 + lane;                    // row of the tile == TMEM lane
@@ -613,6 +625,10 @@ void launch_gemm(const CUtensorMap& tmap, const GemmParams& p, int64_t max_tiles
     if (dev >= 64 || !attr_set[dev]) {
         B200_CUDA(cudaFuncSetAttribute(moe_gemm_kernel<STAGE, PT, ACT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        kSmemBytes));
+        cudaFuncAttributes fa;
+        B200_CUDA(cudaFuncGetAttributes(&fa, moe_gemm_kernel<STAGE, PT, ACT>));
+        B200_CHECK((int64_t)fa.numRegs * kThreads >= kRegDemand, "GEMM kernel was compiled with ", fa.numRegs,
+                   " registers per thread: its roles' setmaxnreg requests (", kRegDemand, " per CTA) could never be met");
         if (dev < 64) attr_set[dev] = true;
     }
     B200_CHECK(sm_margin < sm_count(dev), "sm_margin (", sm_margin, ") must leave at least one of the device's ",

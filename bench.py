@@ -475,11 +475,24 @@ def main():
     ap.add_argument("--ep-placement", default="balanced", choices=["contiguous", "balanced"],
                     help="N>1: experts in contiguous slices per rank, or placed by the route counts of a calibration "
                          "batch (other seed) so that every rank gets the same number of experts and a level load")
+    ap.add_argument("--ep-graph", default="auto", choices=["auto", "on", "off"],
+                    help="N>1: replay the expert-parallel layer call from a captured CUDA graph (one driver call per "
+                         "step instead of ~14 launches from Python); auto = on, falling back to eager launches on "
+                         "all ranks if the capture fails on any")
     ap.add_argument("--cuda-profiler-range", action="store_true",
                     help="bracket the device-timed steps with cudaProfilerStart/Stop (ncu --profile-from-start off)")
+    ap.add_argument("--library-fp8-gemm-only", type=int, default=0, metavar="N",
+                    help="run nothing but the vendor library's dense e4m3 GEMM (N^3) and print its rate: the known "
+                         "workload a profiler's tensor-pipe counters are calibrated on")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
+    if args.library_fp8_gemm_only:
+        n = args.library_fp8_gemm_only
+        tf = library_fp8_gemm_tflops(torch.device("cuda", 0), n=n, iters=5)
+        print(json.dumps({"library_fp8_gemm": f"torch._scaled_mm {n}^3 e4m3, tensor-wise scales, bf16 out",
+                          "tflops": tf, "flops_per_launch": 2.0 * n ** 3}))
+        return
     args.warmup = max(args.warmup, 3)
     small = args.tokens != M_PREFILL or args.experts != E
     if small:
@@ -557,8 +570,30 @@ def main():
         def layer(a, b, c):
             return ep.ep_fused_moe(a, w1_q, w2_q, b, c, w1_s, w2_s, E, exchange=exchange, expert_rank=xr)
 
+    eager_layer, captured = layer, None
+    if world > 1 and args.ep_graph != "off":
+        from aiter_b200.graph import CapturedLayer
+        err = None
+        try:
+            captured = CapturedLayer(eager_layer, dx, dtw, dti)
+        except Exception as e:   # noqa: BLE001 - any failure means "launch eagerly", agreed on by all ranks below
+            err = f"{type(e).__name__}: {e}"
+        ok = torch.tensor([0 if err else 1], dtype=torch.int32, device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 0:
+            if args.ep_graph == "on":
+                raise RuntimeError(f"--ep-graph on: capture failed ({err or 'on another rank'})")
+            print(f"[bench] rank {rank}: graph capture not used ({err or 'failed on another rank'})", file=sys.stderr)
+            captured = None
+        else:
+            def layer(a, b, c):
+                # new inputs are copied into the captured tensors; the result is copied out of the captured output,
+                # which the next replay overwrites
+                return captured(a, b, c).clone()
+
     def step_dev():
-        return layer(dx, dtw, dti)
+        # inputs resident in HBM: with a captured graph they are the captured input tensors themselves
+        return captured.replay() if captured is not None else layer(dx, dtw, dti)
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -569,7 +604,7 @@ def main():
     stage_marks, fm.kernel_bench_events = fm.kernel_bench_events, None
     t_e2e_total = timed_e2e_pipelined(layer, (hx, htw, hti), hout2, dev, args.steps, min(args.warmup, 3), sync)
     launches0 = _lib.launch_count
-    step_dev()
+    eager_layer(dx, dtw, dti)   # a graph replay issues the same kernels without passing the counter
     gpu_launches = (_lib.launch_count - launches0) * args.steps * 2   # device-timed and end-to-end loops
     clocks = sampler.stop() if rank == 0 else None
     aiter_b200.check_device_status()
@@ -586,7 +621,9 @@ def main():
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate, bf16 in/out)", "data": "synthetic",
         "config": {"workload": WORKLOAD, "tokens": M_PREFILL, "model_dim": H, "inter_dim": I, "experts": E,
-                   "topk": TOPK, "parallelism": f"ep{world}" + (f" ({exchange} exchange, {args.ep_placement} expert placement)" if world > 1 else ""),
+                   "topk": TOPK, "parallelism": f"ep{world}" + (f" ({exchange} exchange, {args.ep_placement} expert placement, "
+                                                                f"{'CUDA-graph replay' if captured is not None else 'eager launches'})"
+                                                                if world > 1 else ""),
                    "l2_policy": "inputs larger than L2 (11.3 GB of weights per step)"},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": int(hx.numel() * 2 + htw.numel() * 4 + hti.numel() * 4) * world,
@@ -680,7 +717,7 @@ def main():
         n_act = int(torch.unique(tid).numel())
 
         def step_decode():
-            return layer(dxd, dtwd, dtid)
+            return eager_layer(dxd, dtwd, dtid)
 
         td = timed(step_decode, max(args.steps, 20), args.warmup, sync)
         us = max_over_ranks(statistics.median(td) * 1e3)
@@ -706,6 +743,13 @@ def main():
             us_graph = statistics.median(tg) * 1e3
             dec["graph_replay_us"] = us_graph
             dec["graph_replay_frac_of_hbm"] = algorithmic_bytes(M_DECODE, n_act) / (us_graph * 1e-6) / 1e9 / pk["hbm_gbs"]
+        elif captured is not None:
+            cap_dec = CapturedLayer(eager_layer, dxd, dtwd, dtid)   # collective: all ranks capture here
+            tg = timed(cap_dec.replay, max(args.steps, 20), args.warmup, sync)
+            us_graph = max_over_ranks(statistics.median(tg) * 1e3)
+            dec["graph_replay_us"] = us_graph
+            dec["graph_replay_frac_of_hbm"] = (algorithmic_bytes(M_DECODE, max(act_per_rank)) / (us_graph * 1e-6) / 1e9
+                                               / pk["hbm_gbs"])
         line["decode"] = dec
         aiter_b200.check_device_status()
     if world == 1 and not args.no_cpu_baseline:

@@ -49,6 +49,17 @@ def _worker(rank, world, port, ret):
             outp = ep.ep_fused_moe(*args, exchange="p2p")
             sp = moe_oracle.error_stats(outp.cpu(), out.cpu())
             assert not sp["has_nan"] and sp["n_diff"] <= 1e-3 * sp["numel"] and sp["max_abs_over_rms"] <= 0.02, sp
+        # the same peer-memory call (its NCCL collectives included) replayed from a captured CUDA graph, with the
+        # captured inputs and with new ones
+        from aiter_b200.graph import CapturedLayer
+        layer = lambda x, tw, ti: ep.ep_fused_moe(x, args[1], args[2], tw, ti, args[5], args[6], E, exchange="p2p")
+        cap = CapturedLayer(layer, args[0], args[3], args[4])
+        for x, tw, ti in ((args[0], args[3], args[4]),
+                          (args[0].flip(0).contiguous(), args[3].flip(0).contiguous(), args[4].flip(0).contiguous())):
+            outg = cap(x, tw, ti).clone()
+            oute = layer(x, tw, ti)
+            sg = moe_oracle.error_stats(outg.cpu(), oute.cpu())
+            assert not sg["has_nan"] and sg["n_diff"] <= 1e-3 * sg["numel"] and sg["max_abs_over_rms"] <= 0.02, sg
         torch.cuda.synchronize()
         aiter_b200.check_device_status()
         ret[rank] = out.cpu()
