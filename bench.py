@@ -603,6 +603,19 @@ def main():
     t_dev = timed(step_dev, args.steps, args.warmup, sync, profile=args.cuda_profiler_range)
     stage_marks, fm.kernel_bench_events = fm.kernel_bench_events, None
     t_e2e_total = timed_e2e_pipelined(layer, (hx, htw, hti), hout2, dev, args.steps, min(args.warmup, 3), sync)
+    # the two host copies of a step timed alone (what bounds e2e when they are slower than the layer)
+    def copy_ms(pairs, reps=3):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            for dst, src in pairs:
+                dst.copy_(src, non_blocking=True)
+        e1.record()
+        e1.synchronize()
+        return e0.elapsed_time(e1) / reps
+    h2d_ms = max_over_ranks(copy_ms([(dx, hx), (dtw, htw), (dti, hti)]))
+    d2h_ms = max_over_ranks(copy_ms([(hout, step_dev())]))
     launches0 = _lib.launch_count
     eager_layer(dx, dtw, dti)   # a graph replay issues the same kernels without passing the counter
     gpu_launches = (_lib.launch_count - launches0) * args.steps * 2   # device-timed and end-to-end loops
@@ -628,6 +641,7 @@ def main():
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
                 "h2d_bytes_per_step": int(hx.numel() * 2 + htw.numel() * 4 + hti.numel() * 4) * world,
                 "d2h_bytes_per_step": int(hout.numel() * 2) * world,
+                "h2d_ms_alone": round(h2d_ms, 4), "d2h_ms_alone": round(d2h_ms, 4),
                 "how": "pinned host -> device copy of x, topk_weight, topk_ids and device -> pinned host copy of the bf16 "
                        "result every step, on two copy streams overlapping the neighbouring steps' compute"},
         "clocks": clocks,
