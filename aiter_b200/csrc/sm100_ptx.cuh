@@ -182,21 +182,6 @@ __device__ __forceinline__ void tmem_ld_x16_sync(uint32_t taddr, uint32_t* r) {
         : "memory");
 }
 
-// 8 columns, no wait: the registers may be read only after tmem_wait_ld8 on the same array
-__device__ __forceinline__ void tmem_ld_x8(uint32_t taddr, uint32_t* r) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(taddr)
-                 : "memory");
-}
-// waits for all TMEM loads of this thread; the array is an in/out operand so that no use of it moves above the wait
-__device__ __forceinline__ void tmem_wait_ld8(uint32_t* r) {
-    asm volatile("tcgen05.wait::ld.sync.aligned;"
-                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7])
-                 :
-                 : "memory");
-}
-
 __device__ __forceinline__ float rcp_approx(float x) {
     float y;
     asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));

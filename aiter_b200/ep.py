@@ -57,26 +57,65 @@ def expert_mask_for_rank(num_experts: int, rank: int, world: int, device=None, e
     return mask
 
 
-def balanced_expert_placement(route_counts, world: int) -> torch.Tensor:
-    """Expert -> rank table [E] int32 with E/world experts per rank and the per-rank route totals levelled:
-    experts in descending order of ``route_counts`` (routes per expert on a calibration batch) each go to the
-    rank with the smallest total that still has a free slot. What a weight loader would run once, from routing
+def balanced_expert_placement(route_counts, world: int, method: str = "swap", tolerance: float = 0.02) -> torch.Tensor:
+    """Expert -> rank table [E] int32 with E/world experts per rank and the per-rank route totals levelled, from
+    ``route_counts`` (routes per expert on a calibration batch). What a weight loader would run once, from routing
     statistics, to place the experts; contiguous slices leave the hottest rank 1.4x above the mean on the
-    DeepSeek-V3 benchmark routing."""
+    DeepSeek-V3 benchmark routing.
+
+    ``method="lpt"``: experts in descending order of their counts each go to the rank with the smallest total that
+    still has a free slot. Levels best, but scatters the experts of a routing group over all ranks, so a token with
+    group-limited routing then has routes on more ranks and more rows travel in dispatch and combine.
+    ``method="swap"``: starts from the contiguous slices (one routing group per rank when groups == ranks) and
+    exchanges one expert of the most loaded rank with one of another rank, the pair that levels those two ranks best,
+    until the most loaded rank is within ``tolerance`` of the mean or no exchange helps: the fewest experts leave
+    their group."""
     counts = torch.as_tensor(route_counts).to(torch.int64).cpu()
     E = counts.numel()
     if E % world != 0:
         raise ValueError(f"num_experts ({E}) must be divisible by the EP world size ({world})")
     per = E // world
-    load = [0] * world
-    free = [per] * world
-    table = torch.empty(E, dtype=torch.int32)
-    for e in torch.argsort(counts, descending=True, stable=True).tolist():
-        r = min((r for r in range(world) if free[r] > 0), key=lambda r: (load[r], r))
-        table[e] = r
-        load[r] += int(counts[e])
-        free[r] -= 1
-    return table
+    if method == "lpt":
+        load = [0] * world
+        free = [per] * world
+        table = torch.empty(E, dtype=torch.int32)
+        for e in torch.argsort(counts, descending=True, stable=True).tolist():
+            r = min((r for r in range(world) if free[r] > 0), key=lambda r: (load[r], r))
+            table[e] = r
+            load[r] += int(counts[e])
+            free[r] -= 1
+        return table
+    if method != "swap":
+        raise ValueError(f"method must be 'lpt' or 'swap', got {method!r}")
+    c = counts.tolist()
+    owner = [e // per for e in range(E)]
+    load = [sum(c[r * per:(r + 1) * per]) for r in range(world)]
+    mean = sum(load) / world
+    for _ in range(4 * E):
+        hi = max(range(world), key=lambda r: (load[r], -r))
+        if load[hi] <= mean * (1.0 + tolerance):
+            break
+        best = None   # (resulting max of the two ranks, expert of hi, expert of the other rank)
+        for lo in range(world):
+            if lo == hi or load[lo] >= load[hi]:
+                continue
+            gap = load[hi] - load[lo]
+            for a in (e for e in range(E) if owner[e] == hi):
+                for b in (e for e in range(E) if owner[e] == lo):
+                    d = c[a] - c[b]
+                    if 0 < d < gap:
+                        after = max(load[hi] - d, load[lo] + d)
+                        if best is None or after < best[0]:
+                            best = (after, a, b)
+        if best is None:
+            break
+        _, a, b = best
+        lo = owner[b]
+        d = c[a] - c[b]
+        owner[a], owner[b] = lo, hi
+        load[hi] -= d
+        load[lo] += d
+    return torch.tensor(owner, dtype=torch.int32)
 
 
 def local_experts_of(expert_rank, rank: int) -> torch.Tensor:

@@ -472,9 +472,10 @@ def main():
     ap.add_argument("--ep-exchange", default="auto", choices=["auto", "nccl", "p2p"],
                     help="N>1: NCCL all-gather + fp32 reduce-scatter, or dispatch/combine over peer memory; auto = "
                          "peer memory if every rank can map its peers' buffers, else NCCL")
-    ap.add_argument("--ep-placement", default="balanced", choices=["contiguous", "balanced"],
+    ap.add_argument("--ep-placement", default="balanced", choices=["contiguous", "balanced", "lpt"],
                     help="N>1: experts in contiguous slices per rank, or placed by the route counts of a calibration "
-                         "batch (other seed) so that every rank gets the same number of experts and a level load")
+                         "batch (other seed) so that every rank gets the same number of experts and a level load: "
+                         "balanced = the fewest experts exchanged between the slices, lpt = greedy from scratch")
     ap.add_argument("--ep-graph", default="auto", choices=["auto", "on", "off"],
                     help="N>1: replay the expert-parallel layer call from a captured CUDA graph (one driver call per "
                          "step instead of ~14 launches from Python); auto = on, falling back to eager launches on "
@@ -543,9 +544,10 @@ def main():
     # as a loader would place experts from routing statistics; rank r holds its experts in ascending global id
     table = torch.arange(E, dtype=torch.int32) // (E // world)
     placement_info = None
-    if world > 1 and args.ep_placement == "balanced":
+    if world > 1 and args.ep_placement != "contiguous":
         _xc, _twc, tic = make_tokens(M_PREFILL, seed=100, device=dev, bias=router_inputs(M_PREFILL)[2])
-        table = ep.balanced_expert_placement(torch.bincount(tic.flatten().long(), minlength=E), world)
+        table = ep.balanced_expert_placement(torch.bincount(tic.flatten().long(), minlength=E), world,
+                                             method="swap" if args.ep_placement == "balanced" else "lpt")
     if world > 1:
         counts = torch.bincount(ti.flatten().long(), minlength=E)
         load = torch.zeros(world, dtype=torch.long).index_add_(0, table.long(), counts)
@@ -553,7 +555,7 @@ def main():
         placement_info = {"kind": args.ep_placement, "routes_per_rank": load.tolist(),
                           "max_over_mean": float(load.max()) / (float(load.sum()) / world),
                           "mean_ranks_per_token": float(ranks_per_token.float().mean())}
-    xr = table.to(dev) if (world > 1 and args.ep_placement == "balanced") else None
+    xr = table.to(dev) if (world > 1 and args.ep_placement != "contiguous") else None
 
     exchange = args.ep_exchange
     if world > 1 and exchange == "auto":
