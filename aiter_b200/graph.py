@@ -47,8 +47,18 @@ class CapturedLayer:
         if not isinstance(self.output, torch.Tensor):
             raise TypeError("CapturedLayer: fn must return one tensor")
 
+    def release(self):
+        """Destroys the captured graph and drops its tensors. A graph that holds captured collectives must be
+        released before the process group is destroyed (the communicator's teardown otherwise waits for ever on
+        the work the graph still references); a collective point like the construction."""
+        if self.graph is not None:
+            self.graph.reset()
+        self.graph, self.output, self.inputs = None, None, ()
+
     def replay(self):
         """Runs the captured launches on the current stream with whatever ``inputs`` hold now."""
+        if self.graph is None:
+            raise RuntimeError("CapturedLayer: replay after release()")
         self.graph.replay()
         return self.output
 

@@ -572,7 +572,7 @@ def main():
         def layer(a, b, c):
             return ep.ep_fused_moe(a, w1_q, w2_q, b, c, w1_s, w2_s, E, exchange=exchange, expert_rank=xr)
 
-    eager_layer, captured = layer, None
+    eager_layer, captured, cap_dec = layer, None, None
     if world > 1 and args.ep_graph != "off":
         from aiter_b200.graph import CapturedLayer
         err = None
@@ -778,10 +778,24 @@ def main():
 
     if rank == 0:
         emit(line)
+        sys.stdout.flush()
     if world > 1:
+        # The result is out. Teardown order: captured graphs (they reference the communicator's work), the peer
+        # mappings, then the process group; a teardown that does not finish within 30 s ends the process with status 0
+        # instead of holding N GPUs until the launcher's limit.
+        import threading
+        guard = threading.Timer(30.0, os._exit, (0,))
+        guard.daemon = True
+        guard.start()
+        torch.cuda.synchronize()
         dist.barrier()
+        for cap in (captured, cap_dec):
+            if cap is not None:
+                cap.release()
+        torch.cuda.synchronize()
         ep.PeerExchange.clear()
         dist.destroy_process_group()
+        guard.cancel()
 
 
 if __name__ == "__main__":
