@@ -12,7 +12,7 @@ DEV = "cuda:0"
 
 
 def test_captured_layer_replays_with_new_inputs():
-    c = inputs.make_config("cfg0", seed=3, device=DEV)
+    c = inputs.make_config("cfg0", seed=3)   # on the host: the oracle reads it there
     w = {k: c[k].to(DEV) for k in ("w1_q", "w2_q", "w1_scale", "w2_scale")}
 
     def layer(x, tw, ti):
@@ -21,7 +21,7 @@ def test_captured_layer_replays_with_new_inputs():
 
     x, tw, ti = c["x"].to(DEV), c["topk_weight"].to(DEV), c["topk_ids"].to(DEV)
     cap = CapturedLayer(layer, x, tw, ti)
-    ref = moe_oracle.fused_moe_ref(c["x"], c["w1_q"].cpu(), c["w1_scale"].cpu(), c["w2_q"].cpu(), c["w2_scale"].cpu(),
+    ref = moe_oracle.fused_moe_ref(c["x"], c["w1_q"], c["w1_scale"], c["w2_q"], c["w2_scale"],
                                    c["topk_weight"], c["topk_ids"])
     s = moe_oracle.error_stats(cap(x, tw, ti).cpu(), ref.cpu())
     assert not s["has_nan"] and s["frac_within"] >= 0.995 and s["max_abs_over_rms"] <= 0.02, s
