@@ -52,6 +52,7 @@ _SIGNATURES = {
     "b200_moe_finalize": (ctypes.c_int, [_T] * 2 + [ctypes.c_void_p]),
     "b200_moe_quant_per_tensor": (ctypes.c_int, [_T] * 6 + [ctypes.c_void_p]),
     "b200_ep_dispatch": (ctypes.c_int, [_T] * 5 + [ctypes.c_int] * 3 + [_T, ctypes.c_void_p]),
+    "b200_ep_quant_dispatch": (ctypes.c_int, [_T] * 4 + [ctypes.c_int] * 3 + [_T, ctypes.c_void_p]),
     "b200_ep_push_partials": (ctypes.c_int, [_T] * 3 + [ctypes.c_int] * 3 + [_T, ctypes.c_void_p]),
     "b200_ep_combine": (ctypes.c_int, [_T] * 4 + [ctypes.c_int] * 3 + [_T, ctypes.c_void_p]),
     "b200_ep_ipc_export": (ctypes.c_int, [_T, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64)]),

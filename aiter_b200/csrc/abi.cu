@@ -41,6 +41,8 @@ void launch_ep_push(const aiter_tensor_t*, const aiter_tensor_t*, const aiter_te
                     cudaStream_t);
 void launch_ep_combine(aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, int, int, int,
                        const aiter_tensor_t*, cudaStream_t);
+void launch_ep_quant_dispatch(const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, int,
+                              int, int, const aiter_tensor_t*, cudaStream_t);
 void launch_ep_dispatch(const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*,
                         const aiter_tensor_t*, int, int, int, const aiter_tensor_t*, cudaStream_t);
 void ipc_export(const aiter_tensor_t*, void*, int64_t*);
@@ -251,6 +253,17 @@ B200_EXPORT int b200_ep_dispatch(const aiter_tensor_t* a1, const aiter_tensor_t*
         DeviceGuard g(a1->device_id);
         launch_ep_dispatch(a1, a1_scale, topk_ids, peer_a1, peer_a1_scale, rank, world, experts_per_rank, expert_rank,
                            (cudaStream_t)stream);
+    });
+}
+
+B200_EXPORT int b200_ep_quant_dispatch(const aiter_tensor_t* input, const aiter_tensor_t* topk_ids, const aiter_tensor_t* peer_a1,
+                                       const aiter_tensor_t* peer_a1_scale, int rank, int world, int experts_per_rank,
+                                       const aiter_tensor_t* expert_rank, void* stream) {
+    return safe_call([&] {
+        B200_CHECK(input != nullptr, "input must not be NULL");
+        DeviceGuard g(input->device_id);
+        launch_ep_quant_dispatch(input, topk_ids, peer_a1, peer_a1_scale, rank, world, experts_per_rank, expert_rank,
+                                 (cudaStream_t)stream);
     });
 }
 

@@ -30,6 +30,7 @@
 #include <cuda_fp16.h>
 
 #include "common.cuh"
+#include "quant_device.cuh"
 
 namespace b200 {
 namespace {
@@ -86,6 +87,40 @@ __global__ void __launch_bounds__(kEpThreads) ep_dispatch_kernel(const uint4* __
             uint32_t* ds = reinterpret_cast<uint32_t*>(peer_a1s[r]) + t * KB;
             for (int i = threadIdx.x; i < H16; i += kEpThreads) dq[i] = a1[(size_t)tl * H16 + i];
             for (int i = threadIdx.x; i < KB; i += kEpThreads) ds[i] = a1s[(size_t)tl * KB + i];
+        }
+    }
+    __threadfence_system();
+}
+
+// Quantise-and-dispatch in one kernel: the 1x128 quantisation of a local token row (same arithmetic as the plain
+// quantiser, quant_device.cuh) whose codes and scales are stored straight into the arenas of the ranks that hold one
+// of the token's experts; the quantised row never exists in this rank's own memory unless this rank is among them.
+// One CTA per token, 16 lanes per 128-element group, 8-byte peer stores (a warp's 32 lanes write 256 contiguous
+// bytes), the group's scale by its first lane.
+template <bool F16>
+__global__ void __launch_bounds__(kEpThreads) ep_quant_dispatch_kernel(const uint4* __restrict__ x, const int* __restrict__ topk_ids,
+                                                                       const long long* __restrict__ peer_a1,
+                                                                       const long long* __restrict__ peer_a1s, int m_local, int KB,
+                                                                       int topk, int rank, int world, int experts_per_rank,
+                                                                       const int* __restrict__ expert_rank) {
+    const int sub = threadIdx.x & 15;
+    const int passes = (KB + kEpThreads / 16 - 1) / (kEpThreads / 16);   // the same trip count for every thread
+    for (int tl = blockIdx.x; tl < m_local; tl += gridDim.x) {
+        const unsigned long long m = touch_mask(topk_ids + (size_t)tl * topk, topk, experts_per_rank, world, expert_rank);
+        const size_t t = (size_t)rank * m_local + tl;
+        for (int i = 0; i < passes; ++i) {
+            const int g = i * (kEpThreads / 16) + (threadIdx.x >> 4);
+            const bool live = g < KB;
+            uint4 raw = make_uint4(0, 0, 0, 0);
+            if (live) raw = __ldg(x + ((size_t)tl * KB + g) * 16 + sub);
+            uint2 codes;
+            const float scale = quant_group16<F16>(raw, codes);
+            if (!live) continue;
+            for (int r = 0; r < world; ++r) {
+                if (!((m >> r) & 1ull)) continue;
+                reinterpret_cast<uint2*>(peer_a1[r])[(t * KB + g) * 16 + sub] = codes;
+                if (sub == 0) reinterpret_cast<float*>(peer_a1s[r])[t * KB + g] = scale;
+            }
         }
     }
     __threadfence_system();
@@ -165,6 +200,30 @@ void launch_ep_dispatch(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale
                                                        (const long long*)peer_a1_scale->ptr, (int)m_local, (int)(H / 16),
                                                        (int)KB, (int)topk_ids->shape[1], rank, world, experts_per_rank,
                                                        rank_table(expert_rank));
+    B200_CUDA(cudaGetLastError());
+}
+
+void launch_ep_quant_dispatch(const aiter_tensor_t* x, const aiter_tensor_t* topk_ids, const aiter_tensor_t* peer_a1,
+                              const aiter_tensor_t* peer_a1_scale, int rank, int world, int experts_per_rank,
+                              const aiter_tensor_t* expert_rank, cudaStream_t stream) {
+    check_tensor(x, "input", -1, 2);
+    B200_CHECK(x->dtype_ == AITER_DTYPE_bf16 || x->dtype_ == AITER_DTYPE_fp16, "input must be bf16 or fp16");
+    check_tensor(topk_ids, "topk_ids", AITER_DTYPE_i32, 2);
+    check_tensor(peer_a1, "peer_a1", AITER_DTYPE_i64, 1);
+    check_tensor(peer_a1_scale, "peer_a1_scale", AITER_DTYPE_i64, 1);
+    const int64_t m_local = x->shape[0], H = x->shape[1];
+    B200_CHECK(topk_ids->shape[0] == m_local, "topk_ids rows must match the input");
+    B200_CHECK(world >= 1 && world <= kMaxWorld && rank >= 0 && rank < world, "bad rank/world: ", rank, "/", world);
+    B200_CHECK(experts_per_rank >= 1, "experts_per_rank must be positive");
+    B200_CHECK((int64_t)peer_a1->numel_ == world && (int64_t)peer_a1_scale->numel_ == world,
+               "peer tables need one address per rank");
+    B200_CHECK(H % 128 == 0 && ((uintptr_t)x->ptr & 15) == 0, "rows must be multiples of 128 elements and 16-byte aligned");
+    if (m_local == 0) return;
+    const int grid = (int)std::min<int64_t>(m_local, (int64_t)sm_count(x->device_id) * 8);
+    auto kern = x->dtype_ == AITER_DTYPE_fp16 ? ep_quant_dispatch_kernel<true> : ep_quant_dispatch_kernel<false>;
+    kern<<<grid, kEpThreads, 0, stream>>>((const uint4*)x->ptr, (const int*)topk_ids->ptr, (const long long*)peer_a1->ptr,
+                                          (const long long*)peer_a1_scale->ptr, (int)m_local, (int)(H / 128),
+                                          (int)topk_ids->shape[1], rank, world, experts_per_rank, rank_table(expert_rank));
     B200_CUDA(cudaGetLastError());
 }
 

@@ -13,31 +13,10 @@
 #include <cuda_fp8.h>
 
 #include "common.cuh"
+#include "quant_device.cuh"
 
 namespace b200 {
 namespace {
-
-// eight 16-bit floats (bf16 or fp16) of one 16-byte load -> fp32
-template <bool F16>
-__device__ __forceinline__ void unpack8(const uint4& raw, float (&v)[8]) {
-    if (F16) {
-        const __half2* h = reinterpret_cast<const __half2*>(&raw);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float2 f = __half22float2(h[i]);
-            v[2 * i] = f.x;
-            v[2 * i + 1] = f.y;
-        }
-    } else {
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float2 f = __bfloat1622float2(h[i]);
-            v[2 * i] = f.x;
-            v[2 * i + 1] = f.y;
-        }
-    }
-}
 
 constexpr int kQuantThreads = 256;
 constexpr int kGroupsPerBlock = kQuantThreads / 16;
@@ -57,26 +36,10 @@ __global__ void __launch_bounds__(kQuantThreads) quant_1x128_kernel(
     const bool live = g < rows_used * groups_per_row;
     uint4 raw = make_uint4(0, 0, 0, 0);
     if (live) raw = __ldg(x + g * 16 + sub);
-    float v[8];
-    unpack8<F16>(raw, v);
-    float amax = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-#pragma unroll
-    for (int d = 8; d >= 1; d >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, d));
-    float scale = __fdiv_rn(amax, 448.0f);
-    if (scale == 0.f) scale = 1.f;
-    uint32_t w[2];
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-        float2 lo = make_float2(__fdiv_rn(v[4 * i], scale), __fdiv_rn(v[4 * i + 1], scale));
-        float2 hi = make_float2(__fdiv_rn(v[4 * i + 2], scale), __fdiv_rn(v[4 * i + 3], scale));
-        uint32_t a = __nv_cvt_float2_to_fp8x2(lo, __NV_SATFINITE, __NV_E4M3);
-        uint32_t b = __nv_cvt_float2_to_fp8x2(hi, __NV_SATFINITE, __NV_E4M3);
-        w[i] = a | (b << 16);
-    }
+    uint2 codes;
+    const float scale = quant_group16<F16>(raw, codes);
     if (live) {
-        q[g * 16 + sub] = make_uint2(w[0], w[1]);
+        q[g * 16 + sub] = codes;
         if (sub == 0) {
             const int64_t row = g / groups_per_row, cg = g - row * groups_per_row;
             scales[transposed ? cg * rows_used + row : g] = scale;

@@ -283,13 +283,18 @@ def ep_fused_moe(x_local, w1_local, w2_local, topk_weight_local, topk_ids_local,
         raise NotImplementedError("ep_fused_moe: the peer-memory exchange carries 1x128 scales; use exchange='nccl' "
                                   "with QuantType.per_Token")
     layer_kw = {} if quant_type == QuantType.per_1x128 else {"quant_type": quant_type}
-    _mark(timers, "ep_quant")
-    a1_l, a1s_l = quant(x_local) if quant_type == QuantType.per_1x128 else quant(x_local, quant_type)
-    a1s_l = a1s_l.view(m_local, -1)
-    _mark(timers, "ep_all_gather")
     ex = None
     if exchange not in ("nccl", "p2p"):
         raise ValueError(f"exchange must be 'nccl' or 'p2p', got {exchange!r}")
+    # peer-memory exchange with the library's own quantiser: one kernel quantises a row and stores it on the ranks
+    # that need it (the quantised row never exists here unless this rank is one of them)
+    fused_dispatch = (world > 1 and exchange == "p2p" and quant is _gpu_quant
+                      and x_local.dtype in (dtypes.bf16, dtypes.fp16))
+    _mark(timers, "ep_quant")
+    if not fused_dispatch:
+        a1_l, a1s_l = quant(x_local) if quant_type == QuantType.per_1x128 else quant(x_local, quant_type)
+        a1s_l = a1s_l.view(m_local, -1)
+    _mark(timers, "ep_all_gather")
     if world == 1:
         a1, a1s, ids, wts = a1_l, a1s_l, topk_ids_local, topk_weight_local
     elif exchange == "p2p":
@@ -298,8 +303,12 @@ def ep_fused_moe(x_local, w1_local, w2_local, topk_weight_local, topk_ids_local,
         # means every rank's rows have landed
         ex = PeerExchange.get(group, m_local, H, dev)
         ids_l = topk_ids_local.contiguous()
-        _lib.call("b200_ep_dispatch", a1_l, a1s_l.view(m_local, -1), ids_l, ex.ptrs_a1, ex.ptrs_a1_scale, rank, world,
-                  num_experts // world, expert_rank, device=dev)
+        if fused_dispatch:
+            _lib.call("b200_ep_quant_dispatch", x_local.contiguous(), ids_l, ex.ptrs_a1, ex.ptrs_a1_scale, rank, world,
+                      num_experts // world, expert_rank, device=dev)
+        else:
+            _lib.call("b200_ep_dispatch", a1_l, a1s_l.view(m_local, -1), ids_l, ex.ptrs_a1, ex.ptrs_a1_scale, rank, world,
+                      num_experts // world, expert_rank, device=dev)
         side_l = torch.cat([ids_l.view(torch.int32), topk_weight_local.contiguous().view(torch.int32)], dim=1)
         side = torch.empty((world * m_local, side_l.shape[1]), dtype=torch.int32, device=dev)
         dist.all_gather_into_tensor(side, side_l, group=group)

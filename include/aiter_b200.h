@@ -202,6 +202,11 @@ int b200_moe_finalize(aiter_tensor_t* out, const aiter_tensor_t* acc, void* stre
 int b200_ep_dispatch(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale, const aiter_tensor_t* topk_ids,
                      const aiter_tensor_t* peer_a1, const aiter_tensor_t* peer_a1_scale, int rank, int world,
                      int experts_per_rank, const aiter_tensor_t* expert_rank, void* stream);
+/* The same dispatch fused with the 1x128 quantisation that precedes it (b200_moe_quant_1x128's arithmetic): input
+ * [M/G, model_dim] bf16 or fp16; the codes and scales go straight into the peers' buffers. */
+int b200_ep_quant_dispatch(const aiter_tensor_t* input, const aiter_tensor_t* topk_ids, const aiter_tensor_t* peer_a1,
+                           const aiter_tensor_t* peer_a1_scale, int rank, int world, int experts_per_rank,
+                           const aiter_tensor_t* expert_rank, void* stream);
 int b200_ep_push_partials(const aiter_tensor_t* acc, const aiter_tensor_t* topk_ids, const aiter_tensor_t* peer_recv,
                           int rank, int world, int experts_per_rank, const aiter_tensor_t* expert_rank, void* stream);
 int b200_ep_combine(aiter_tensor_t* out, const aiter_tensor_t* acc, const aiter_tensor_t* recv,

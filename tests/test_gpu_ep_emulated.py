@@ -17,12 +17,13 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-@pytest.mark.parametrize("world,routing,E,topk,placement", [
-    (2, "softmax", 8, 2, "contiguous"), (4, "zipf", 8, 2, "contiguous"),
-    (8, "dsv3", 64, 8, "contiguous"),   # the benchmark's structure in small: 8 groups = 8 ranks, routes on <= 4 of them
-    (4, "zipf", 8, 2, "balanced"), (8, "dsv3", 64, 8, "balanced"),   # expert -> rank table levelled by route counts
+@pytest.mark.parametrize("world,routing,E,topk,placement,fused", [
+    (2, "softmax", 8, 2, "contiguous", False), (4, "zipf", 8, 2, "contiguous", True),
+    (8, "dsv3", 64, 8, "contiguous", False),   # the benchmark's structure in small: 8 groups = 8 ranks, routes on <= 4 of them
+    (8, "dsv3", 64, 8, "contiguous", True),    # fused: one kernel quantises the rows and stores them on the peers
+    (4, "zipf", 8, 2, "balanced", False), (8, "dsv3", 64, 8, "balanced", True),   # expert -> rank table levelled by route counts
 ])
-def test_dispatch_push_combine_emulated_ranks(world, routing, E, topk, placement):
+def test_dispatch_push_combine_emulated_ranks(world, routing, E, topk, placement, fused):
     M, H, I = 256, 512, 256
     g = torch.Generator().manual_seed(world)
     x = torch.randn((M, H), generator=g).to(torch.bfloat16)
@@ -56,6 +57,10 @@ def test_dispatch_push_combine_emulated_ranks(world, routing, E, topk, placement
     # 1. dispatch: every rank stores its rows where they are needed
     for r in range(world):
         rows = slice(r * m_local, (r + 1) * m_local)
+        if fused:
+            _lib.call("b200_ep_quant_dispatch", x[rows].contiguous(), ti[rows].contiguous(), p_a1, p_a1s, r, world, epr, xr,
+                      device=dev)
+            continue
         q, s = per_group_quant_hip(x[rows], quant_dtype=torch.float8_e4m3fn)
         _lib.call("b200_ep_dispatch", q, s, ti[rows].contiguous(), p_a1, p_a1s, r, world, epr, xr, device=dev)
     # rows arrived exactly where a route exists
