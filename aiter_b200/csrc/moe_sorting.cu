@@ -15,7 +15,7 @@
 //   single CTA   routes <= kSingleMaxRoutes: count, scan, fill and scatter in one kernel;
 //   multi CTA    count per 4096-route chunk -> scan (1 CTA) -> scatter per chunk, with the
 //                per-chunk counts and expert bases in a caller-provided workspace.
-// Extra CTAs of the first kernel zero-fill moe_buf when the caller passes one.
+// Extra CTAs zero-fill moe_buf when the caller passes one (in the single kernel, or beside the scan).
 
 #include "common.cuh"
 
@@ -234,10 +234,6 @@ __global__ void __launch_bounds__(kThreads, 1) sort_single_kernel(SortArgs a) {
 }
 
 __global__ void __launch_bounds__(kThreads, 1) sort_count_kernel(SortArgs a) {
-    if ((int)blockIdx.x >= a.nchunks) {
-        zero_fill(a, blockIdx.x - a.nchunks, gridDim.x - a.nchunks);
-        return;
-    }
     int* hist = smem_i;
     const int routes = eff_tokens(a) * a.topk;
     const int r0 = min((int)blockIdx.x * kChunk, routes);
@@ -248,6 +244,13 @@ __global__ void __launch_bounds__(kThreads, 1) sort_count_kernel(SortArgs a) {
 }
 
 __global__ void __launch_bounds__(kThreads, 1) sort_scan_kernel(SortArgs a) {
+    // CTA 0 scans; the others zero-fill moe_buf beside it. The scan is one CTA's worth of latency (tens of
+    // microseconds at 64 K routes), the fill is bandwidth: in the same launch the fill costs nothing extra, in the
+    // count kernel (which is over in microseconds) it would delay the two kernels behind it by its whole length.
+    if (blockIdx.x >= 1) {
+        zero_fill(a, blockIdx.x - 1, gridDim.x - 1);
+        return;
+    }
     int* local_id = smem_i;
     int* base = local_id + a.E;
     int* warp_tot = base + a.E;
@@ -403,8 +406,8 @@ void launch_moe_sorting(const aiter_tensor_t* topk_ids, const aiter_tensor_t* to
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_full));
         B200_CUDA(cudaFuncSetAttribute(sort_scatter_kernel,
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_full));
-        sort_count_kernel<<<a.nchunks + zero_ctas, kThreads, smem_full, stream>>>(a);
-        sort_scan_kernel<<<1, kThreads, (2 * (size_t)E + 40) * sizeof(int), stream>>>(a);
+        sort_count_kernel<<<a.nchunks, kThreads, smem_full, stream>>>(a);
+        sort_scan_kernel<<<1 + zero_ctas, kThreads, (2 * (size_t)E + 40) * sizeof(int), stream>>>(a);
         sort_scatter_kernel<<<a.nchunks, kThreads, smem_full, stream>>>(a);
     }
     B200_CUDA(cudaGetLastError());

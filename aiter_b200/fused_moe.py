@@ -296,10 +296,12 @@ def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, 
         timers = kernel_bench_events
 
     _mark(timers, "sort")
-    # stage 2 accumulates into its own fp32 buffer, so no zero-filled moe_buf is asked for
-    sorted_ids, sorted_weights, sorted_expert_ids, num_valid_ids, _ = _moe_sorting_impl(
-        topk_ids, topk_weight, global_E, model_dim, dtypes.bf16, GEMM_BLOCK_M, expert_mask,
-        num_local_tokens, 0, False, want_moe_buf=False)
+    # stage 2 accumulates fp32 sums: the sort's zero-filled moe_buf, asked for as [M, model_dim] fp32, is that
+    # accumulator (its spare CTAs clear it beside the scan, so no fill kernel of its own runs); the column-range
+    # variant has another layout and clears its own
+    sorted_ids, sorted_weights, sorted_expert_ids, num_valid_ids, acc_buf = _moe_sorting_impl(
+        topk_ids, topk_weight, global_E, model_dim, dtypes.fp32, GEMM_BLOCK_M, expert_mask,
+        num_local_tokens, 0, False, want_moe_buf=stage2_chunks == 1)
     _mark(timers, "quant")
     # per_Tensor runs through the per_Token kernels: the one activation scale is repeated per row, the one weight
     # scale per expert is repeated per output channel (the reference dequantises both types the same way,
@@ -355,7 +357,7 @@ def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, 
                 on_chunk(c, acc[c])
         _mark(timers, "end")
         return acc
-    acc = torch.zeros((M, model_dim), dtype=dtypes.fp32, device=device)
+    acc = acc_buf
     _mark(timers, "stage2")
     _lib.call("b200_moe_stage2", a2, a2_s, w2, w2_scale, sorted_ids, sorted_weights, sorted_expert_ids,
               num_valid_ids, acc, status, 0, 0, 0, qt, dw2, device=device)

@@ -98,6 +98,13 @@ def test_moe_buf_is_zeroed_and_placeholder():
     w, ids = inputs.make_routing("softmax", 9001, 8, 2, seed=2)
     *_, buf = aiter_b200.moe_sorting(ids.to(DEV), w.to(DEV), 8, 3, torch.float16, 32)
     assert buf.shape == (9001, 3) and int((buf.view(torch.int16) != 0).sum()) == 0
+    # the fp32 accumulator of the layer: cleared beside the scan kernel, whatever the pool held before
+    del buf
+    dirty = torch.full((9001 * 512,), float("nan"), device=DEV)
+    del dirty
+    *_, buf = aiter_b200.moe_sorting(ids.to(DEV), w.to(DEV), 8, 512, torch.float32, 128)
+    assert buf.shape == (9001, 512) and buf.dtype == torch.float32
+    assert int((buf.view(torch.int32) != 0).sum()) == 0
 
 
 def test_errors_are_reported_not_crashed():
