@@ -53,7 +53,7 @@ _SIGNATURES = {
     "b200_moe_quant_per_tensor": (ctypes.c_int, [_T] * 6 + [ctypes.c_void_p]),
     "b200_ep_dispatch": (ctypes.c_int, [_T] * 5 + [ctypes.c_int] * 3 + [_T, ctypes.c_void_p]),
     "b200_ep_quant_dispatch": (ctypes.c_int, [_T] * 4 + [ctypes.c_int] * 3 + [_T, ctypes.c_void_p]),
-    "b200_ep_push_partials": (ctypes.c_int, [_T] * 3 + [ctypes.c_int] * 3 + [_T, ctypes.c_void_p]),
+    "b200_ep_push_partials": (ctypes.c_int, [_T] * 3 + [ctypes.c_int] * 3 + [_T] + [ctypes.c_int] * 3 + [ctypes.c_void_p]),
     "b200_ep_combine": (ctypes.c_int, [_T] * 4 + [ctypes.c_int] * 3 + [_T, ctypes.c_void_p]),
     "b200_ep_ipc_export": (ctypes.c_int, [_T, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int64)]),
     "b200_ep_ipc_open": (ctypes.c_int, [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(ctypes.c_int64)]),
@@ -82,7 +82,7 @@ def lib():
             fn = getattr(handle, name)  # AttributeError if the symbol is not exported
             fn.restype = res
             fn.argtypes = args
-        if handle.aiter_ctypes_abi_version() != 3:
+        if handle.aiter_ctypes_abi_version() != 4:
             raise RuntimeError("libaiter_b200.so: unexpected C-ABI version")
         _lib = handle
     return _lib

@@ -38,7 +38,7 @@ void launch_biased_grouped_topk(const aiter_tensor_t*, const aiter_tensor_t*, ai
                                 int, float, cudaStream_t);
 void launch_topk_softmax(aiter_tensor_t*, aiter_tensor_t*, aiter_tensor_t*, const aiter_tensor_t*, int, cudaStream_t);
 void launch_ep_push(const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, int, int, int, const aiter_tensor_t*,
-                    cudaStream_t);
+                    int, int, int, cudaStream_t);
 void launch_ep_combine(aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, int, int, int,
                        const aiter_tensor_t*, cudaStream_t);
 void launch_ep_quant_dispatch(const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, const aiter_tensor_t*, int,
@@ -100,7 +100,7 @@ using namespace b200;
 
 extern "C" {
 
-B200_EXPORT int aiter_ctypes_abi_version(void) { return 3; }
+B200_EXPORT int aiter_ctypes_abi_version(void) { return 4; }
 
 B200_EXPORT const char* aiter_get_last_error(void) { return last_error().empty() ? nullptr : last_error().c_str(); }
 
@@ -269,11 +269,13 @@ B200_EXPORT int b200_ep_quant_dispatch(const aiter_tensor_t* input, const aiter_
 
 B200_EXPORT int b200_ep_push_partials(const aiter_tensor_t* acc, const aiter_tensor_t* topk_ids,
                                       const aiter_tensor_t* peer_recv, int rank, int world, int experts_per_rank,
-                                      const aiter_tensor_t* expert_rank, void* stream) {
+                                      const aiter_tensor_t* expert_rank, int col_begin, int col_end, int sm_limit,
+                                      void* stream) {
     return safe_call([&] {
         B200_CHECK(acc != nullptr, "acc must not be NULL");
         DeviceGuard g(acc->device_id);
-        launch_ep_push(acc, topk_ids, peer_recv, rank, world, experts_per_rank, expert_rank, (cudaStream_t)stream);
+        launch_ep_push(acc, topk_ids, peer_recv, rank, world, experts_per_rank, expert_rank, col_begin, col_end, sm_limit,
+                       (cudaStream_t)stream);
     });
 }
 

@@ -57,7 +57,9 @@ __device__ __forceinline__ unsigned long long touch_mask(const int* __restrict__
 __global__ void __launch_bounds__(kEpThreads) ep_push_kernel(const float4* __restrict__ acc, const int* __restrict__ topk_ids,
                                                              const long long* __restrict__ peer_recv, int M, int H4,
                                                              int topk, int rank, int world, int experts_per_rank,
-                                                             int m_local, const int* __restrict__ expert_rank) {
+                                                             int m_local, const int* __restrict__ expert_rank, int c0, int c1) {
+    // columns [c0, c1) of every row, in 16-byte units: a launch per column range lets the caller push a finished range
+    // of stage 2 while the next one is computed
     for (int t = blockIdx.x; t < M; t += gridDim.x) {
         const int owner = t / m_local;
         if (owner == rank) continue;
@@ -65,7 +67,7 @@ __global__ void __launch_bounds__(kEpThreads) ep_push_kernel(const float4* __res
         if (!((m >> rank) & 1ull)) continue;
         const float4* src = acc + (size_t)t * H4;
         float4* dst = reinterpret_cast<float4*>(peer_recv[owner]) + ((size_t)rank * m_local + (t - owner * m_local)) * H4;
-        for (int i = threadIdx.x; i < H4; i += kEpThreads) dst[i] = src[i];
+        for (int i = c0 + threadIdx.x; i < c1; i += kEpThreads) dst[i] = src[i];
     }
     __threadfence_system();   // the peer stores are performed before this kernel counts as complete
 }
@@ -228,16 +230,25 @@ void launch_ep_quant_dispatch(const aiter_tensor_t* x, const aiter_tensor_t* top
 }
 
 void launch_ep_push(const aiter_tensor_t* acc, const aiter_tensor_t* topk_ids, const aiter_tensor_t* peer_recv, int rank,
-                    int world, int experts_per_rank, const aiter_tensor_t* expert_rank, cudaStream_t stream) {
+                    int world, int experts_per_rank, const aiter_tensor_t* expert_rank, int col_begin, int col_end,
+                    int sm_limit, cudaStream_t stream) {
     int64_t M, H, topk, m_local;
     check_common(acc, topk_ids, rank, world, experts_per_rank, M, H, topk, m_local);
     check_tensor(peer_recv, "peer_recv", AITER_DTYPE_i64, 1);
     B200_CHECK((int64_t)peer_recv->numel_ == world, "peer_recv needs one address per rank");
+    if (col_end <= 0) col_end = (int)H;
+    B200_CHECK(col_begin >= 0 && col_begin < col_end && col_end <= H && col_begin % 4 == 0 && col_end % 4 == 0,
+               "column range [", col_begin, ", ", col_end, ") must lie in [0, model_dim] on 4-column boundaries");
+    B200_CHECK(sm_limit >= 0, "sm_limit must not be negative");
     if (M == 0 || world == 1) return;
-    const int grid = (int)std::min<int64_t>(M, (int64_t)sm_count(acc->device_id) * 8);
+    // sm_limit > 0: at most that many SMs' worth of CTAs (8 per SM), for a push that runs beside a GEMM kernel on the
+    // SMs the GEMM leaves free
+    const int sms = sm_limit > 0 ? std::min(sm_limit, sm_count(acc->device_id)) : sm_count(acc->device_id);
+    const int grid = (int)std::min<int64_t>(M, (int64_t)sms * 8);
     ep_push_kernel<<<grid, kEpThreads, 0, stream>>>((const float4*)acc->ptr, (const int*)topk_ids->ptr,
                                                    (const long long*)peer_recv->ptr, (int)M, (int)(H / 4), (int)topk, rank,
-                                                   world, experts_per_rank, (int)m_local, rank_table(expert_rank));
+                                                   world, experts_per_rank, (int)m_local, rank_table(expert_rank),
+                                                   col_begin / 4, col_end / 4);
     B200_CUDA(cudaGetLastError());
 }
 

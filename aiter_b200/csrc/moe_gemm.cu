@@ -754,7 +754,10 @@ void launch_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* a2_scale,
     B200_CHECK(col_begin >= 0 && col_begin < col_end && col_end <= H && col_begin % 256 == 0 &&
                    (col_end % 256 == 0 || col_end == H),
                "column range [", col_begin, ", ", col_end, ") must lie in [0, model_dim] on 256-column boundaries");
-    B200_CHECK(acc->shape[1] == col_end - col_begin, "acc must be [M, col_end - col_begin]");
+    // acc is either the range's own block [M, col_end - col_begin] or the whole [M, model_dim] buffer, of which
+    // this launch then fills columns [col_begin, col_end)
+    const bool full_width = acc->shape[1] == H;
+    B200_CHECK(full_width || acc->shape[1] == col_end - col_begin, "acc must be [M, col_end - col_begin] or [M, model_dim]");
     B200_CHECK(((uintptr_t)acc->ptr & 15) == 0, "acc must be 16-byte aligned (bulk reductions)");
     B200_CHECK(sm_margin >= 0, "sm_margin must not be negative");
     B200_CHECK(I % 128 == 0 && H % 128 == 0, "inter_dim and model_dim must be multiples of 128");
@@ -789,10 +792,10 @@ void launch_moe_stage2(const aiter_tensor_t* a2, const aiter_tensor_t* a2_scale,
     p.KB = (int)(I / 128);
     p.n_tiles = (col_end - col_begin + 255) / 256;
     p.nt0 = col_begin / 256;
-    p.acc_ld = col_end - col_begin;
+    p.acc_ld = full_width ? (int)H : col_end - col_begin;
     p.n_rows = (int)H;
     p.inter = (int)I;
-    p.acc = (float*)acc->ptr;
+    p.acc = (float*)acc->ptr + (full_width ? col_begin : 0);
     p.status = (int*)status->ptr;
     p.use_weight = doweight != 0;
     CUtensorMap tmap = make_weight_map(w2->ptr, (uint64_t)(E * H), (uint64_t)I);

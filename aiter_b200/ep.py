@@ -124,11 +124,11 @@ def local_experts_of(expert_rank, rank: int) -> torch.Tensor:
 
 
 def _gpu_local_layer(a1, a1_scale, w1, w2, topk_weight, topk_ids, expert_mask, w1_scale, w2_scale, timers=None,
-                     chunks=1, on_chunk=None, sm_margin=0, quant_type=QuantType.per_1x128):
+                     chunks=1, on_chunk=None, sm_margin=0, quant_type=QuantType.per_1x128, ranges=1):
     """All rows, local experts -> fp32 partial [M, H] (or [chunks, M, H/chunks]); no final rounding."""
     return fused_moe_stages(a1, w1, w2, topk_weight, topk_ids, expert_mask, w1_scale, w2_scale,
                             a1_scale, None, None, timers=timers, stage2_chunks=chunks, on_chunk=on_chunk,
-                            sm_margin=sm_margin, quant_type=quant_type)
+                            sm_margin=sm_margin, quant_type=quant_type, stage2_ranges=ranges)
 
 
 def _gpu_quant(x, quant_type=QuantType.per_1x128):
@@ -141,6 +141,17 @@ def _gpu_finalize(acc, dtype):
     out = torch.empty(acc.shape, dtype=dtype, device=acc.device)
     _lib.call("b200_moe_finalize", out, acc, device=acc.device)
     return out
+
+
+_STREAMS: dict = {}
+
+
+def _side_streams(device):
+    """(high-priority stream for the GEMM launches, stream for the pushes) of ``device``, created once."""
+    key = device.index
+    if key not in _STREAMS:
+        _STREAMS[key] = (torch.cuda.Stream(device=device, priority=-1), torch.cuda.Stream(device=device))
+    return _STREAMS[key]
 
 
 class PeerExchange:
@@ -237,13 +248,16 @@ class PeerExchange:
         cls._opened.clear()
 
 
-def _p2p_combine(ex, partial, ids, num_experts, group, dtype, timers, expert_rank=None):
-    """partial [M, H] fp32 of this rank -> out [M/G, H]: push, barrier, combine."""
+def _p2p_combine(ex, partial, ids, num_experts, group, dtype, timers, expert_rank=None, pushed=False):
+    """partial [M, H] fp32 of this rank -> out [M/G, H]: push (unless the caller pushed the column ranges already),
+    barrier, combine."""
     world, rank = dist.get_world_size(group), dist.get_rank(group)
     M, H = partial.shape
     m_local = M // world
     epr = num_experts // world
-    _lib.call("b200_ep_push_partials", partial, ids, ex.ptrs_recv, rank, world, epr, expert_rank, device=partial.device)
+    if not pushed:
+        _lib.call("b200_ep_push_partials", partial, ids, ex.ptrs_recv, rank, world, epr, expert_rank, 0, 0, 0,
+                  device=partial.device)
     _mark(timers, "ep_barrier")
     dist.all_reduce(ex.flag, group=group)   # passes only after every rank's push kernel has completed
     _mark(timers, "ep_combine")
@@ -262,6 +276,9 @@ def ep_fused_moe(x_local, w1_local, w2_local, topk_weight_local, topk_ids_local,
     column ranges and the reduce-scatter of a finished range is issued beside the computation of the next;
     ``sm_margin`` SMs are kept free for NCCL during those launches. Off by default: on 8 B200s four ranges
     of 59 MB took as long in total as one 235 MB reduce-scatter after the unsplit stage 2 (1.47 vs 1.40 ms).
+    With ``exchange="p2p"`` and ``overlap_chunks`` > 1 stage 2 fills the partial in that many column ranges and the push of
+    a finished range runs beside the next range, on the ``sm_margin`` SMs that launch leaves idle (the local-layer
+    timers are not recorded in this mode).
     ``exchange``: "nccl" = fp32 reduce-scatter of the partials; "p2p" = push of the produced rows into the
     owner's memory + combine (see the module docstring; the first call builds the IPC mappings).
     ``expert_rank``: optional [num_experts] int32 device tensor, the rank that owns each expert (a placement from
@@ -332,7 +349,31 @@ def ep_fused_moe(x_local, w1_local, w2_local, topk_weight_local, topk_ids_local,
     if overlap_chunks is None:
         overlap_chunks = 1   # measured on 8 x B200: the ranged reduce-scatters gain nothing over one call
     if overlap_chunks > 1 and ex is not None:
-        raise ValueError("overlap_chunks > 1 belongs to the NCCL exchange")
+        # Peer-memory exchange: stage 2 fills the [M, H] partial in column ranges and the push of a finished range
+        # runs beside the next range. The GEMM launches go to a high-priority stream, so that when a range's push and
+        # the next range's GEMM become ready together the GEMM's CTAs are placed first and the push takes the SMs
+        # that launch leaves idle (a GEMM CTA needs a whole SM; behind resident push CTAs it would wait for them).
+        main = torch.cuda.current_stream(dev)
+        gemm_stream, push_stream = _side_streams(dev)
+        epr = num_experts // world
+
+        def on_range(c, block):
+            acc, c0, c1 = block
+            push_stream.wait_stream(gemm_stream)
+            with torch.cuda.stream(push_stream):
+                _lib.call("b200_ep_push_partials", acc, ids, ex.ptrs_recv, rank, world, epr, expert_rank, c0, c1,
+                          sm_margin if c + 1 < overlap_chunks else 0, device=dev)
+
+        gemm_stream.wait_stream(main)
+        with torch.cuda.stream(gemm_stream):
+            partial = local_layer(a1, a1s, w1_local, w2_local, wts, ids, mask, w1_scale_local, w2_scale_local,
+                                  ranges=overlap_chunks, on_chunk=on_range, sm_margin=sm_margin, **layer_kw)
+        main.wait_stream(gemm_stream)
+        main.wait_stream(push_stream)
+        _mark(timers, "ep_push")
+        out = _p2p_combine(ex, partial, ids, num_experts, group, dtype, timers, expert_rank, pushed=True)
+        _mark(timers, "end")
+        return out
     if overlap_chunks > 1:
         # column ranges: the reduce-scatter of range c runs (on NCCL's stream) beside stage 2 of range c+1
         hc = H // overlap_chunks

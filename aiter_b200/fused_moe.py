@@ -276,7 +276,7 @@ def _mark(timers, name):
 def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, w1_scale, w2_scale,
                      a1_scale, num_local_tokens, dtype, return_intermediates=False, timers=None,
                      stage2_chunks=1, on_chunk=None, sm_margin=0, quant_type=QuantType.per_1x128,
-                     activation=ActivationType.Silu, doweight_stage1=False):
+                     activation=ActivationType.Silu, doweight_stage1=False, stage2_ranges=1):
     """sort -> a1 quant -> stage 1 -> stage 2 -> final rounding (the 2-stage flow of
     aiter/fused_moe.py:2979-3368 with the requant fused into stage 1).
 
@@ -284,6 +284,10 @@ def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, 
     its own contiguous fp32 block of the returned [chunks, M, H/chunks] tensor, calling
     ``on_chunk(index, block)`` after each launch so the caller can start a collective on it while the
     next range is computed; ``sm_margin`` SMs are left idle by those launches for the collective's kernels.
+
+    ``stage2_ranges`` > 1 (with ``dtype=None``) also computes the output columns in that many ranges, but into the one
+    [M, H] buffer: ``on_chunk(index, (acc, col_begin, col_end))`` is called after each launch, and the launches after the
+    first leave ``sm_margin`` SMs idle (the first has nothing running beside it).
 
     ``timers``: optional list that receives (name, cuda event) marks recorded on the current
     stream before each kernel and at the end (the reference's per-stage bench hook,
@@ -302,6 +306,8 @@ def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, 
     sorted_ids, sorted_weights, sorted_expert_ids, num_valid_ids, acc_buf = _moe_sorting_impl(
         topk_ids, topk_weight, global_E, model_dim, dtypes.fp32, GEMM_BLOCK_M, expert_mask,
         num_local_tokens, 0, False, want_moe_buf=stage2_chunks == 1)
+    if stage2_chunks > 1 and stage2_ranges > 1:
+        raise ValueError("stage2_chunks and stage2_ranges exclude each other")
     _mark(timers, "quant")
     # per_Tensor runs through the per_Token kernels: the one activation scale is repeated per row, the one weight
     # scale per expert is repeated per output channel (the reference dequantises both types the same way,
@@ -359,6 +365,18 @@ def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, 
         return acc
     acc = acc_buf
     _mark(timers, "stage2")
+    if stage2_ranges > 1:
+        if dtype is not None or model_dim % (256 * stage2_ranges) != 0:
+            raise ValueError("stage2_ranges needs dtype=None and model_dim divisible by 256*ranges")
+        hc = model_dim // stage2_ranges
+        for c in range(stage2_ranges):
+            _lib.call("b200_moe_stage2", a2, a2_s, w2, w2_scale, sorted_ids, sorted_weights, sorted_expert_ids,
+                      num_valid_ids, acc, status, c * hc, (c + 1) * hc, int(sm_margin) if c > 0 else 0, qt, dw2,
+                      device=device)
+            if on_chunk is not None:
+                on_chunk(c, (acc, c * hc, (c + 1) * hc))
+        _mark(timers, "end")
+        return acc
     _lib.call("b200_moe_stage2", a2, a2_s, w2, w2_scale, sorted_ids, sorted_weights, sorted_expert_ids,
               num_valid_ids, acc, status, 0, 0, 0, qt, dw2, device=device)
     if dtype is None:        # caller wants the fp32 sums (expert parallelism reduces them across ranks first)

@@ -476,6 +476,9 @@ def main():
                     help="N>1: experts in contiguous slices per rank, or placed by the route counts of a calibration "
                          "batch (other seed) so that every rank gets the same number of experts and a level load: "
                          "balanced = the fewest experts exchanged between the slices, lpt = greedy from scratch")
+    ap.add_argument("--ep-push-ranges", type=int, default=1,
+                    help="N>1, peer-memory exchange: stage 2 in this many column ranges, the push of a finished range "
+                         "beside the GEMM of the next (1 = one stage-2 launch, then one push)")
     ap.add_argument("--ep-graph", default="auto", choices=["auto", "on", "off"],
                     help="N>1: replay the expert-parallel layer call from a captured CUDA graph (one driver call per "
                          "step instead of ~14 launches from Python); auto = on, falling back to eager launches on "
@@ -569,8 +572,11 @@ def main():
         def layer(a, b, c):
             return aiter_b200.fused_moe(a, w1_q, w2_q, b, c, quant_type=QT.per_1x128, w1_scale=w1_s, w2_scale=w2_s)
     else:
+        ranges = args.ep_push_ranges if exchange == "p2p" else 1
+
         def layer(a, b, c):
-            return ep.ep_fused_moe(a, w1_q, w2_q, b, c, w1_s, w2_s, E, exchange=exchange, expert_rank=xr)
+            return ep.ep_fused_moe(a, w1_q, w2_q, b, c, w1_s, w2_s, E, exchange=exchange, expert_rank=xr,
+                                   overlap_chunks=ranges)
 
     eager_layer, captured, cap_dec = layer, None, None
     if world > 1 and args.ep_graph != "off":
@@ -637,7 +643,8 @@ def main():
         "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate, bf16 in/out)", "data": "synthetic",
         "config": {"workload": WORKLOAD, "tokens": M_PREFILL, "model_dim": H, "inter_dim": I, "experts": E,
                    "topk": TOPK, "parallelism": f"ep{world}" + (f" ({exchange} exchange, {args.ep_placement} expert placement, "
-                                                                f"{'CUDA-graph replay' if captured is not None else 'eager launches'})"
+                                                                f"{'CUDA-graph replay' if captured is not None else 'eager launches'}"
+                                                                + (f", push in {ranges} column ranges beside stage 2" if ranges > 1 else "") + ")"
                                                                 if world > 1 else ""),
                    "l2_policy": "inputs larger than L2 (11.3 GB of weights per step)"},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "ms_per_step": ms_e2e,

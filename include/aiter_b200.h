@@ -54,7 +54,7 @@ typedef struct aiter_tensor_t {
 } aiter_tensor_t;
 
 /* csrc/include/aiter_ctypes_error.h:61-71 */
-int         aiter_ctypes_abi_version(void); /* == 3 */
+int         aiter_ctypes_abi_version(void); /* == 4 */
 const char* aiter_get_last_error(void);     /* NULL when no error is pending */
 void        aiter_clear_last_error(void);
 
@@ -158,7 +158,8 @@ int b200_moe_stage1(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale,
  * per token in fp32.  Replaces ck_moe_stage2
  * (csrc/ck_gemm_moe_2stages_codegen/gemm_moe_ck2stages.cu:139-199).
  *   a2/a2_scale as written by stage 1; w2 [E,H,I] fp8 + w2_scale [E,H/128,I/128] fp32
- *   acc [M, col_end-col_begin] fp32, must be zero on entry; receives sum over routes of weight * (a2 . w2)
+ *   acc [M, col_end-col_begin] fp32 (the range's own block) or [M, model_dim] (the whole buffer, of which columns
+ *   [col_begin, col_end) are filled), zero on entry; receives sum over routes of weight * (a2 . w2)
  *   for the output columns [col_begin, col_end) (multiples of 256; col_end <= 0 means model_dim). Launching
  *   the columns in several ranges lets a caller hand finished ranges to a collective while the next is computed;
  *   sm_margin SMs are then left idle by this launch so that the collective's kernels can run beside it.
@@ -207,8 +208,11 @@ int b200_ep_dispatch(const aiter_tensor_t* a1, const aiter_tensor_t* a1_scale, c
 int b200_ep_quant_dispatch(const aiter_tensor_t* input, const aiter_tensor_t* topk_ids, const aiter_tensor_t* peer_a1,
                            const aiter_tensor_t* peer_a1_scale, int rank, int world, int experts_per_rank,
                            const aiter_tensor_t* expert_rank, void* stream);
+/* col_begin/col_end: push only these columns of every row (0, 0 = all), so that a finished column range of stage 2
+ * can travel while the next range is computed; sm_limit > 0 bounds the launch to that many SMs' worth of CTAs. */
 int b200_ep_push_partials(const aiter_tensor_t* acc, const aiter_tensor_t* topk_ids, const aiter_tensor_t* peer_recv,
-                          int rank, int world, int experts_per_rank, const aiter_tensor_t* expert_rank, void* stream);
+                          int rank, int world, int experts_per_rank, const aiter_tensor_t* expert_rank, int col_begin,
+                          int col_end, int sm_limit, void* stream);
 int b200_ep_combine(aiter_tensor_t* out, const aiter_tensor_t* acc, const aiter_tensor_t* recv,
                     const aiter_tensor_t* topk_ids, int rank, int world, int experts_per_rank,
                     const aiter_tensor_t* expert_rank, void* stream);

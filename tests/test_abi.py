@@ -50,7 +50,7 @@ def test_ctypes_signatures_match_header(lib):
 
 
 def test_abi_version_and_error_channel(lib):
-    assert lib.aiter_ctypes_abi_version() == 3
+    assert lib.aiter_ctypes_abi_version() == 4
     lib.aiter_clear_last_error()
     assert lib.aiter_get_last_error() is None
     # a call with a NULL tensor fails with status -1 and a message, without touching a GPU

@@ -78,10 +78,18 @@ def test_dispatch_push_combine_emulated_ranks(world, routing, E, topk, placement
     for r in range(world):
         sl = ep.local_experts_of(table_cpu, r).to(dev)   # the rank's experts, ascending global id
         mask = ep.expert_mask_for_rank(E, r, world, device=dev, expert_rank=xr)
+        # fused cases: stage 2 in two column ranges into the one [M, H] buffer
+        seen = []
         partial.append(fused_moe_stages(a1_all[r], w1_q[sl].contiguous(), w2_q[sl].contiguous(), tw, ti, mask,
-                                        w1_s[sl].contiguous(), w2_s[sl].contiguous(), a1s_all[r], None, None))
+                                        w1_s[sl].contiguous(), w2_s[sl].contiguous(), a1s_all[r], None, None,
+                                        stage2_ranges=2 if fused else 1, on_chunk=lambda c, blk: seen.append(blk[1:])))
+        assert seen == ([(0, H // 2), (H // 2, H)] if fused else [])
     for r in range(world):
-        _lib.call("b200_ep_push_partials", partial[r], ti, p_recv, r, world, epr, xr, device=dev)
+        if fused:   # in two column ranges, the second on a bounded number of SMs, as the overlapped exchange does
+            _lib.call("b200_ep_push_partials", partial[r], ti, p_recv, r, world, epr, xr, 0, H // 2, 0, device=dev)
+            _lib.call("b200_ep_push_partials", partial[r], ti, p_recv, r, world, epr, xr, H // 2, H, 16, device=dev)
+        else:
+            _lib.call("b200_ep_push_partials", partial[r], ti, p_recv, r, world, epr, xr, 0, 0, 0, device=dev)
     outs = []
     for r in range(world):
         out = torch.empty((m_local, H), dtype=torch.bfloat16, device=dev)

@@ -49,10 +49,15 @@ def _worker(rank, world, port, ret):
             outp = ep.ep_fused_moe(*args, exchange="p2p")
             sp = moe_oracle.error_stats(outp.cpu(), out.cpu())
             assert not sp["has_nan"] and sp["n_diff"] <= 1e-3 * sp["numel"] and sp["max_abs_over_rms"] <= 0.02, sp
+        # stage 2 in two column ranges, the push of the first beside the GEMM of the second (two side streams)
+        outr = ep.ep_fused_moe(*args, exchange="p2p", overlap_chunks=2)
+        sr = moe_oracle.error_stats(outr.cpu(), outp.cpu())
+        assert not sr["has_nan"] and sr["n_diff"] <= 1e-3 * sr["numel"] and sr["max_abs_over_rms"] <= 0.02, sr
         # the same peer-memory call (its NCCL collectives included) replayed from a captured CUDA graph, with the
         # captured inputs and with new ones
         from aiter_b200.graph import CapturedLayer
-        layer = lambda x, tw, ti: ep.ep_fused_moe(x, args[1], args[2], tw, ti, args[5], args[6], E, exchange="p2p")
+        layer = lambda x, tw, ti: ep.ep_fused_moe(x, args[1], args[2], tw, ti, args[5], args[6], E, exchange="p2p",
+                                                  overlap_chunks=2)
         cap = CapturedLayer(layer, args[0], args[3], args[4])
         for x, tw, ti in ((args[0], args[3], args[4]),
                           (args[0].flip(0).contiguous(), args[3].flip(0).contiguous(), args[4].flip(0).contiguous())):
