@@ -476,7 +476,7 @@ def main():
                     help="N>1: experts in contiguous slices per rank, or placed by the route counts of a calibration "
                          "batch (other seed) so that every rank gets the same number of experts and a level load: "
                          "balanced = the fewest experts exchanged between the slices, lpt = greedy from scratch")
-    ap.add_argument("--ep-push-ranges", type=int, default=1,
+    ap.add_argument("--ep-push-ranges", type=int, default=2,
                     help="N>1, peer-memory exchange: stage 2 in this many column ranges, the push of a finished range "
                          "beside the GEMM of the next (1 = one stage-2 launch, then one push)")
     ap.add_argument("--ep-graph", default="auto", choices=["auto", "on", "off"],
