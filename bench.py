@@ -693,6 +693,13 @@ def main():
             for (n0, e0), (_n1, e1) in zip(timers[:-1], timers[1:]):
                 accb.setdefault(n0, []).append(e0.elapsed_time(e1))
         line["ep_breakdown_ms_rank0"] = {k: round(sum(v) / len(v), 4) for k, v in accb.items()}
+        # the same marks of every rank for the parts that depend on the rank's load: who is the slowest, who waits
+        mine_ms = torch.tensor([sum(accb[k]) / len(accb[k]) for k in ("stage1", "stage2", "ep_push", "ep_barrier")],
+                               dtype=torch.float32, device=dev)
+        all_ms = torch.empty((world, 4), dtype=torch.float32, device=dev)
+        dist.all_gather_into_tensor(all_ms, mine_ms)
+        line["ep_ms_per_rank"] = {k: [round(float(v), 4) for v in all_ms[:, i].tolist()]
+                                  for i, k in enumerate(("stage1", "stage2", "ep_push", "ep_barrier"))}
         # host time of one layer call (launches only, no synchronisation): what bounds the step when the device is faster
         torch.cuda.synchronize()
         th = []
