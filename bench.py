@@ -65,6 +65,28 @@ def peaks():
     return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
 
 
+def bind_near_gpu(cuda_index):
+    """Restricts this process to the host cores NVML reports as local to the GPU (its NUMA node), so that the pinned
+    step buffers are allocated on that node and the copy threads run there. Reads NVML only; changes nothing but this
+    process's own CPU affinity. Returns a short description for the bench line."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        pr = torch.cuda.get_device_properties(cuda_index)
+        bus = f"{pr.pci_domain_id:08x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        handle = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode() if hasattr(bus, "encode") else bus)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+        near = {64 * w + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1}
+        allowed = os.sched_getaffinity(0)
+        want = near & allowed
+        if not want or want == allowed:
+            return f"unchanged ({len(allowed)} cores allowed, {len(near)} local to the GPU)"
+        os.sched_setaffinity(0, want)
+        return f"{len(want)} of {len(allowed)} allowed cores, those local to the GPU"
+    except Exception as e:   # noqa: BLE001 - a placement hint: never a reason to fail the bench
+        return f"unchanged ({type(e).__name__}: {e})"
+
+
 class ClockSampler:
     """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
 
@@ -516,6 +538,9 @@ def main():
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    # N > 1: several ranks share the host; each stays on the cores (and memory) of its GPU's NUMA node. N = 1 keeps
+    # all cores: the CPU baseline leg of that line uses them.
+    cpu_affinity = bind_near_gpu(local_rank) if world > 1 else None
     if world > 1:
         import datetime
         # a collective that not every rank reaches ends with an error after this time instead of hanging the job
@@ -658,6 +683,8 @@ def main():
     }
     if placement_info is not None:
         line["expert_placement"] = placement_info
+    if cpu_affinity is not None:
+        line["cpu_affinity_rank0"] = cpu_affinity
 
     if world == 1:
         # per-kernel device time averaged over the timed steps themselves (events recorded inside the timed loop)
