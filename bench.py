@@ -65,6 +65,16 @@ def peaks():
     return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
 
 
+def _nvml_handle(pynvml, cuda_index):
+    """NVML handle of CUDA device ``cuda_index`` (by PCI bus id: the two index spaces differ under CUDA_VISIBLE_DEVICES)."""
+    pr = torch.cuda.get_device_properties(cuda_index)
+    bus = f"{pr.pci_domain_id:08x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+    try:
+        return pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+    except TypeError:
+        return pynvml.nvmlDeviceGetHandleByPciBusId(bus)
+
+
 def bind_near_gpu(cuda_index):
     """Restricts this process to the host cores NVML reports as local to the GPU (its NUMA node), so that the pinned
     step buffers are allocated on that node and the copy threads run there. Reads NVML only; changes nothing but this
@@ -72,9 +82,7 @@ def bind_near_gpu(cuda_index):
     try:
         import pynvml
         pynvml.nvmlInit()
-        pr = torch.cuda.get_device_properties(cuda_index)
-        bus = f"{pr.pci_domain_id:08x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
-        handle = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode() if hasattr(bus, "encode") else bus)
+        handle = _nvml_handle(pynvml, cuda_index)
         words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
         near = {64 * w + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1}
         allowed = os.sched_getaffinity(0)
@@ -99,6 +107,21 @@ class ClockSampler:
         self.gpu = gpu_index
 
     def start(self):
+        # NVML in a thread of this process (what nvidia-smi itself reads): a sample every few milliseconds, so that
+        # even a timed region of some tens of milliseconds (8 ranks) is covered; nvidia-smi -lms as the fallback
+        self.nvml = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.handle = _nvml_handle(pynvml, self.gpu)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.nvml = pynvml
+            self.stop_flag = False
+            self.t = threading.Thread(target=self._poll, daemon=True)
+            self.t.start()
+            return
+        except Exception:   # noqa: BLE001 - any NVML problem: use the command-line tool
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
@@ -108,11 +131,32 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def _poll(self):
+        nv = self.nvml
+        reasons_fn = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+        bits = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
+        while not self.stop_flag:
+            try:
+                mhz = float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                mask = int(reasons_fn(self.handle))
+                self.rows.append([mhz, [n for n, b in bits.items() if mask & b]])
+            except Exception:   # noqa: BLE001
+                pass
+            time.sleep(0.004)
+
     def _read(self):
         for line in self.proc.stdout:
             self.rows.append([c.strip() for c in line.split(",")])
 
     def stop(self):
+        if self.nvml is not None:
+            self.stop_flag = True
+            self.t.join(timeout=2)
+            sm = [r[0] for r in self.rows]
+            names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+            reasons = [n for n in names if any(n in r[1] for r in self.rows)]
+            return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=self.max_mhz, reasons=reasons,
+                        samples=len(sm), source="NVML, one sample per 4 ms")
         if self.proc is None:
             return dict(sm_mhz=None, sm_max_mhz=None, reasons=["nvidia-smi unavailable"])
         self.proc.terminate()
@@ -122,7 +166,7 @@ class ClockSampler:
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i] == "Active" for r in self.rows)]
         return dict(sm_mhz=statistics.median(sm) if sm else None, sm_max_mhz=max(mx) if mx else None,
-                    reasons=reasons, samples=len(sm))
+                    reasons=reasons, samples=len(sm), source="nvidia-smi -lms 100")
 
 
 # ------------------------------------------------------------------------------------------ inputs
