@@ -40,7 +40,7 @@ def _oracle_finalize(acc, dtype):
     return acc.to(dtype)
 
 
-def _worker(rank, world, port, ret):
+def _worker(rank, world, port, ret, placed):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -50,24 +50,38 @@ def _worker(rank, world, port, ret):
         c = inputs.make_config("cfg0", seed=0)
         E, M = c["cfg"]["E"], c["cfg"]["M"]
         per, m_local = E // world, M // world
-        sl = slice(rank * per, (rank + 1) * per)
         rows = slice(rank * m_local, (rank + 1) * m_local)
-        mask = ep.expert_mask_for_rank(E, rank, world)
-        assert int(mask.sum()) == per and bool(mask[sl].all())
+        if placed:
+            # an expert -> rank table levelled by the route counts: the rank's weights are its experts in ascending id
+            table = ep.balanced_expert_placement(torch.bincount(c["topk_ids"].flatten().long(), minlength=E), world,
+                                                 method="lpt")
+            sl = ep.local_experts_of(table, rank)
+            mask = ep.expert_mask_for_rank(E, rank, world, expert_rank=table)
+            assert int(mask.sum()) == per and torch.equal(torch.nonzero(mask).flatten(), sl)
+        else:
+            table = None
+            sl = slice(rank * per, (rank + 1) * per)
+            mask = ep.expert_mask_for_rank(E, rank, world)
+            assert int(mask.sum()) == per and bool(mask[sl].all())
         out = ep.ep_fused_moe(c["x"][rows], c["w1_q"][sl], c["w2_q"][sl], c["topk_weight"][rows],
                               c["topk_ids"][rows], c["w1_scale"][sl], c["w2_scale"][sl], E,
-                              quant=_oracle_quant, local_layer=_oracle_local_layer, finalize=_oracle_finalize)
+                              quant=_oracle_quant, local_layer=_oracle_local_layer, finalize=_oracle_finalize,
+                              expert_rank=table)
         ret[rank] = out
     finally:
         dist.destroy_process_group()
 
 
-def test_ep_two_ranks_matches_single_process_oracle():
+import pytest
+
+
+@pytest.mark.parametrize("placed", [False, True])
+def test_ep_two_ranks_matches_single_process_oracle(placed):
     world = 2
     port = _free_port()
     manager = mp.Manager()
     ret = manager.dict()
-    mp.spawn(_worker, args=(world, port, ret), nprocs=world, join=True)
+    mp.spawn(_worker, args=(world, port, ret, placed), nprocs=world, join=True)
     c = inputs.make_config("cfg0", seed=0)
     ref = moe_oracle.fused_moe_ref(c["x"], c["w1_q"], c["w1_scale"], c["w2_q"], c["w2_scale"],
                                    c["topk_weight"], c["topk_ids"])
@@ -80,6 +94,5 @@ def test_ep_two_ranks_matches_single_process_oracle():
 
 def test_expert_mask_needs_divisible_experts():
     from aiter_b200 import ep
-    import pytest
     with pytest.raises(ValueError, match="divisible"):
         ep.expert_mask_for_rank(10, 0, 4)
