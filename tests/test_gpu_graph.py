@@ -32,7 +32,7 @@ def test_captured_layer_replays_with_new_inputs():
     got = cap(x2, tw2, ti2).clone()
     want = layer(x2, tw2, ti2)
     s2 = moe_oracle.error_stats(got.cpu(), want.cpu())
-    assert not s2["has_nan"] and s2["n_diff"] == s2["n_one_ulp"] and s2["n_diff"] <= 1e-3 * s2["numel"], s2
+    assert not s2["has_nan"] and s2["n_diff"] <= 1e-3 * s2["numel"] and s2["max_abs_excl_one_ulp_over_rms"] <= 1e-3, s2
     # writing into the captured inputs and replaying is the copy-free form
     for dst, src in zip(cap.inputs, (x, tw, ti)):
         dst.copy_(src)
