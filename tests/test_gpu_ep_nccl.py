@@ -14,6 +14,12 @@ from oracle import inputs, moe_oracle
 pytestmark = pytest.mark.gpu
 
 
+def one_ulp_apart(s):
+    """Two runs of the same layer: isolated one-ulp flips (one bf16 ulp of a large element is itself above 2 % of RMS,
+    so the strict figure gets the wider bound), nothing else above 2 % of RMS."""
+    return s["max_abs_excl_one_ulp_over_rms"] <= 0.02 and s["max_abs_over_rms"] <= 0.04
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
@@ -48,11 +54,11 @@ def _worker(rank, world, port, ret):
         for _ in range(2):
             outp = ep.ep_fused_moe(*args, exchange="p2p")
             sp = moe_oracle.error_stats(outp.cpu(), out.cpu())
-            assert not sp["has_nan"] and sp["n_diff"] <= 1e-3 * sp["numel"] and sp["max_abs_over_rms"] <= 0.02, sp
+            assert not sp["has_nan"] and sp["n_diff"] <= 1e-3 * sp["numel"] and one_ulp_apart(sp), sp
         # stage 2 in two column ranges, the push of the first beside the GEMM of the second (two side streams)
         outr = ep.ep_fused_moe(*args, exchange="p2p", overlap_chunks=2)
         sr = moe_oracle.error_stats(outr.cpu(), outp.cpu())
-        assert not sr["has_nan"] and sr["n_diff"] <= 1e-3 * sr["numel"] and sr["max_abs_over_rms"] <= 0.02, sr
+        assert not sr["has_nan"] and sr["n_diff"] <= 1e-3 * sr["numel"] and one_ulp_apart(sr), sr
         # the same peer-memory call (its NCCL collectives included) replayed from a captured CUDA graph, with the
         # captured inputs and with new ones
         from aiter_b200.graph import CapturedLayer
@@ -64,7 +70,7 @@ def _worker(rank, world, port, ret):
             outg = cap(x, tw, ti).clone()
             oute = layer(x, tw, ti)
             sg = moe_oracle.error_stats(outg.cpu(), oute.cpu())
-            assert not sg["has_nan"] and sg["n_diff"] <= 1e-3 * sg["numel"] and sg["max_abs_over_rms"] <= 0.02, sg
+            assert not sg["has_nan"] and sg["n_diff"] <= 1e-3 * sg["numel"] and one_ulp_apart(sg), sg
         torch.cuda.synchronize()
         aiter_b200.check_device_status()
         ret[rank] = out.cpu()

@@ -279,7 +279,8 @@ def test_dsv3_prefill_whole_layer(dsv3_layer):
     out2 = run(c2)
     # fp32 reductions land in a different order on every run: isolated last-bit flips only
     s = moe_oracle.error_stats(out2, (out.float() * 2).to(torch.bfloat16))
-    assert s["n_diff"] <= 1e-3 * s["numel"] and s["max_abs_over_rms"] <= 0.02, s
+    # (one bf16 ulp of an output above 4 is itself 3 % of RMS here: the strict figure gets the wider bound)
+    assert s["n_diff"] <= 1e-3 * s["numel"] and s["max_abs_excl_one_ulp_over_rms"] <= 0.02 and s["max_abs_over_rms"] <= 0.04, s
 
 
 def test_bad_shapes_raise():
