@@ -1,6 +1,6 @@
 """Generates the fixtures in this directory from the UNMODIFIED reference functions.
 
-Needs a checkout of ROCm/aiter (``AITER_REFERENCE_ROOT``, default ``/root/reference``); it
+Needs a checkout of ROCm/aiter (its path in ``AITER_REFERENCE_ROOT``; ``oracle/ref_loader.py`` holds the default); it
 cannot run on a machine without one, which is why its outputs are committed.  For every
 case it also runs the restatement in ``oracle/moe_oracle.py`` on the same inputs and
 asserts bit-identity, so a fixture is only ever written from a pinned oracle.
