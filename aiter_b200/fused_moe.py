@@ -28,17 +28,6 @@ _status_words: dict[int, torch.Tensor] = {}
 _CHECK_STATUS_EVERY_CALL = os.environ.get("AITER_B200_CHECK_STATUS", "0") not in ("", "0")
 
 
-_aux_streams: dict[int, "torch.cuda.Stream"] = {}
-
-
-def _aux_stream(device: torch.device):
-    """Second stream of ``device`` for work that runs beside the caller's stream inside one layer call."""
-    idx = device.index if device.index is not None else torch.cuda.current_device()
-    if idx not in _aux_streams:
-        _aux_streams[idx] = torch.cuda.Stream(device=device)
-    return _aux_streams[idx]
-
-
 def _status(device: torch.device) -> torch.Tensor:
     """Per-device int32 word the GEMM kernels set if a bounded device-side wait runs out."""
     idx = device.index if device.index is not None else torch.cuda.current_device()
@@ -310,23 +299,15 @@ def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, 
     if timers is None:
         timers = kernel_bench_events
 
-    if stage2_chunks > 1 and stage2_ranges > 1:
-        raise ValueError("stage2_chunks and stage2_ranges exclude each other")
     _mark(timers, "sort")
     # stage 2 accumulates fp32 sums: the sort's zero-filled moe_buf, asked for as [M, model_dim] fp32, is that
     # accumulator (its spare CTAs clear it beside the scan, so no fill kernel of its own runs); the column-range
-    # variant has another layout and clears its own.
-    # The sort (latency of three small kernels) and the activation quantiser (bandwidth) do not depend on each other:
-    # when there is something to quantise the sort goes to a second stream and the two run side by side; both are
-    # joined before stage 1. The "sort" mark then measures nothing and the "quant" mark the longer of the two.
-    main = torch.cuda.current_stream(device)
-    side = _aux_stream(device) if hidden_states.dtype != dtypes.fp8 else None
-    if side is not None:
-        side.wait_stream(main)
-    with torch.cuda.stream(side if side is not None else main):
-        sorted_ids, sorted_weights, sorted_expert_ids, num_valid_ids, acc_buf = _moe_sorting_impl(
-            topk_ids, topk_weight, global_E, model_dim, dtypes.fp32, GEMM_BLOCK_M, expert_mask,
-            num_local_tokens, 0, False, want_moe_buf=stage2_chunks == 1)
+    # variant has another layout and clears its own
+    sorted_ids, sorted_weights, sorted_expert_ids, num_valid_ids, acc_buf = _moe_sorting_impl(
+        topk_ids, topk_weight, global_E, model_dim, dtypes.fp32, GEMM_BLOCK_M, expert_mask,
+        num_local_tokens, 0, False, want_moe_buf=stage2_chunks == 1)
+    if stage2_chunks > 1 and stage2_ranges > 1:
+        raise ValueError("stage2_chunks and stage2_ranges exclude each other")
     _mark(timers, "quant")
     # per_Tensor runs through the per_Token kernels: the one activation scale is repeated per row, the one weight
     # scale per expert is repeated per output channel (the reference dequantises both types the same way,
@@ -346,8 +327,6 @@ def fused_moe_stages(hidden_states, w1, w2, topk_weight, topk_ids, expert_mask, 
     else:
         a1, a1_s = per_group_quant_hip(hidden_states, quant_dtype=dtypes.fp8)
 
-    if side is not None:
-        main.wait_stream(side)
     P = sorted_ids.numel()
     status = _status(device)
     _mark(timers, "stage1")
