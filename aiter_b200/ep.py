@@ -272,8 +272,8 @@ def ep_fused_moe(x_local, w1_local, w2_local, topk_weight_local, topk_ids_local,
                  overlap_chunks=None, sm_margin=16, exchange="nccl", quant_type=QuantType.per_1x128, expert_rank=None):
     """x_local [M/G, H] bf16, routing [M/G, topk] with GLOBAL expert ids -> out [M/G, H].
 
-    Every rank must pass the same number of rows. With ``overlap_chunks`` > 1 stage 2 runs in that many
-    column ranges and the reduce-scatter of a finished range is issued beside the computation of the next;
+    Every rank must pass the same number of rows. With the NCCL exchange and ``overlap_chunks`` > 1 stage 2 runs in
+    that many column ranges and the reduce-scatter of a finished range is issued beside the computation of the next;
     ``sm_margin`` SMs are kept free for NCCL during those launches. Off by default: on 8 B200s four ranges
     of 59 MB took as long in total as one 235 MB reduce-scatter after the unsplit stage 2 (1.47 vs 1.40 ms).
     With ``exchange="p2p"`` and ``overlap_chunks`` > 1 stage 2 fills the partial in that many column ranges and the push of
