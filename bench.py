@@ -294,18 +294,23 @@ def timed(fn, steps, warmup, sync, profile=False):
     return [ev[i].elapsed_time(ev[i + 1]) for i in range(steps)]
 
 
-def timed_e2e_pipelined(layer, host_in, host_out2, dev, steps, warmup, sync):
+def timed_e2e_pipelined(layer, host_in, host_out2, dev, steps, warmup, sync, static_out=False):
     """End-to-end steps as a serving loop runs them: every step copies its inputs from pinned host
     memory and its result back to pinned host memory; the copies of neighbouring steps overlap the
     compute on two copy streams (double-buffered device inputs, double-buffered host outputs).
     Returns the total time of `steps` steps in ms (CUDA events on the compute stream, which waits
-    for the last device-to-host copy before the end event)."""
+    for the last device-to-host copy before the end event).
+    ``static_out``: the layer returns the same tensor every step (a replayed graph's output); it is copied into
+    one of two preallocated device buffers before the next replay overwrites it, so the loop allocates nothing."""
     comp = torch.cuda.current_stream(dev)
     s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
     dbuf = [[torch.empty_like(t, device=dev) for t in host_in] for _ in range(2)]
     in_ready = [torch.cuda.Event() for _ in range(2)]
     comp_done = [torch.cuda.Event() for _ in range(2)]
     out_done = [torch.cuda.Event() for _ in range(2)]
+    obuf = [torch.empty(host_out2[0].shape, dtype=host_out2[0].dtype, device=dev) for _ in range(2)] if static_out else None
+    for ev in out_done:
+        ev.record(s_out)
 
     def run(n):
         for i in range(n):
@@ -317,11 +322,16 @@ def timed_e2e_pipelined(layer, host_in, host_out2, dev, steps, warmup, sync):
                 in_ready[b].record(s_in)
             comp.wait_event(in_ready[b])
             out = layer(*dbuf[b])
+            if static_out:
+                comp.wait_event(out_done[b])           # the device-to-host copy that last read this buffer
+                obuf[b].copy_(out, non_blocking=True)
+                out = obuf[b]
             comp_done[b].record(comp)
             with torch.cuda.stream(s_out):
                 s_out.wait_event(comp_done[b])
                 host_out2[b].copy_(out, non_blocking=True)
-                out.record_stream(s_out)
+                if not static_out:
+                    out.record_stream(s_out)
                 out_done[b].record(s_out)
 
     for ev in comp_done:
@@ -664,9 +674,9 @@ def main():
             captured = None
         else:
             def layer(a, b, c):
-                # new inputs are copied into the captured tensors; the result is copied out of the captured output,
-                # which the next replay overwrites
-                return captured(a, b, c).clone()
+                # new inputs are copied into the captured tensors; the result is the captured output tensor, which the
+                # next replay overwrites (the end-to-end loop copies it out first)
+                return captured(a, b, c)
 
     def step_dev():
         # inputs resident in HBM: with a captured graph they are the captured input tensors themselves
@@ -679,7 +689,8 @@ def main():
         fm.kernel_bench_events = []   # per-kernel event marks of the timed steps (warm-up marks are dropped below)
     t_dev = timed(step_dev, args.steps, args.warmup, sync, profile=args.cuda_profiler_range)
     stage_marks, fm.kernel_bench_events = fm.kernel_bench_events, None
-    t_e2e_total = timed_e2e_pipelined(layer, (hx, htw, hti), hout2, dev, args.steps, min(args.warmup, 3), sync)
+    t_e2e_total = timed_e2e_pipelined(layer, (hx, htw, hti), hout2, dev, args.steps, min(args.warmup, 3), sync,
+                                      static_out=captured is not None)
     # the two host copies of a step timed alone (what bounds e2e when they are slower than the layer)
     def copy_ms(pairs, reps=3):
         torch.cuda.synchronize()
